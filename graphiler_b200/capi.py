@@ -1,0 +1,257 @@
+"""ctypes binding of the C ABI in include/gphl.h, with torch tensors as device memory.
+
+This is the Python-side mirror of the operator set the reference registers as ``my_ops::*``
+(src/ops/**): same names, same argument meaning.  There is no CPU path: every function
+requires CUDA tensors and raises if the native library is missing.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p, POINTER
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+LIB_DIR = Path(__file__).resolve().parent / "lib"
+KERNEL_LIB = LIB_DIR / "libgphl.so"
+TORCH_OPS_LIB = LIB_DIR / "libgraphiler.so"
+DEFAULT_CHUNK = 512
+
+_lib = None
+
+# name -> (restype, argtypes); must list every symbol include/gphl.h declares.
+_P = c_void_p
+SIGNATURES = {
+    "gphl_last_error": (c_char_p, []),
+    "gphl_version": (c_int, []),
+    "gphl_launch_count": (c_int64, []),
+    "gphl_plan_create": (c_int, [_P, c_int64, c_int32, c_int64, _P, POINTER(_P)]),
+    "gphl_plan_destroy": (None, [_P]),
+    "gphl_plan_num_items": (c_int64, [_P]),
+    "gphl_plan_num_split_rows": (c_int64, [_P]),
+    "gphl_plan_scratch_bytes": (c_int64, [_P]),
+    "gphl_spmm_gather_sum_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P]),
+    "gphl_spmm_gather_sum_bf16": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P]),
+    "gphl_spmm_u_mul_e_sum_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_sddmm_u_add_v_f32_i64": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_sddmm_u_add_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_sddmm_u_dot_v_f32_i64": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_sddmm_u_dot_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_segment_softmax_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_gat_fused_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, _P, _P, _P, _P]),
+    "gphl_gat_fused_bf16": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, _P, _P, _P]),
+    "gphl_gather_rows_i64": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
+    "gphl_gather_rows_i32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
+    "gphl_segment_mm_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, _P]),
+}
+
+
+class GphlError(RuntimeError):
+    pass
+
+
+def load_library(path: Optional[Path] = None):
+    """dlopen libgphl.so and set the prototypes.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = Path(path) if path else KERNEL_LIB
+    if not p.exists():
+        raise GphlError(f"{p} is missing: run `python -m graphiler_b200.build` (there is no fallback path)")
+    lib = ctypes.CDLL(str(p))
+    for name, (res, args) in SIGNATURES.items():
+        if not hasattr(lib, name):
+            raise GphlError(f"{p} does not export {name}: rebuild with `python -m graphiler_b200.build --force`")
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def lib():
+    return load_library()
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise GphlError(f"{what} failed ({rc}): {lib().gphl_last_error().decode()}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _dev(*ts, dtypes=None):
+    """All tensors must be contiguous CUDA tensors on one device."""
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise GphlError("operators need CUDA tensors (there is no CPU path)")
+        if not t.is_contiguous():
+            raise GphlError("operators need contiguous tensors")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise GphlError("all tensors must live on one device")
+    return dev
+
+
+def launch_count() -> int:
+    return int(lib().gphl_launch_count())
+
+
+class Plan:
+    """Row-split plan for one pointer array (see gphl_plan_create)."""
+
+    def __init__(self, pointer: torch.Tensor, max_feat: int, chunk: int = DEFAULT_CHUNK):
+        _dev(pointer)
+        assert pointer.dtype == torch.int32
+        self._h = c_void_p()
+        self.n_rows = pointer.numel() - 1
+        self.pointer = pointer
+        with torch.cuda.device(pointer.device):
+            _check(lib().gphl_plan_create(_ptr(pointer), self.n_rows, chunk, max_feat, _stream(pointer),
+                                          ctypes.byref(self._h)), "gphl_plan_create")
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def num_items(self):
+        return int(lib().gphl_plan_num_items(self._h))
+
+    @property
+    def num_split_rows(self):
+        return int(lib().gphl_plan_num_split_rows(self._h))
+
+    @property
+    def scratch_bytes(self):
+        return int(lib().gphl_plan_scratch_bytes(self._h))
+
+    def __del__(self):
+        try:
+            if self._h:
+                lib().gphl_plan_destroy(self._h)
+                self._h = c_void_p()
+        except Exception:
+            pass
+
+
+def _h(plan: Optional[Plan]):
+    return None if plan is None else plan.handle
+
+
+def _feat(x: torch.Tensor) -> int:
+    f = 1
+    for s in x.shape[1:]:
+        f *= s
+    return f
+
+
+def spmm_gather_sum(pointer, idx, x, plan: Optional[Plan] = None, out=None):
+    """y[v] = sum over the segment of v of x[idx[i]] (SpMMSrc with node indices, SpMMEdge with edge ids)."""
+    _dev(pointer, idx, x, out)
+    n_rows, f = pointer.numel() - 1, _feat(x)
+    y = out if out is not None else torch.empty((n_rows, f), dtype=x.dtype, device=x.device)
+    fn = {torch.float32: lib().gphl_spmm_gather_sum_f32, torch.bfloat16: lib().gphl_spmm_gather_sum_bf16}[x.dtype]
+    with torch.cuda.device(x.device):
+        _check(fn(_h(plan), _ptr(pointer), _ptr(idx), n_rows, f, _ptr(x), _ptr(y), _stream(x)), "spmm_gather_sum")
+    return y
+
+
+def spmm_u_mul_e_sum(pointer, node_idx, edge_idx, x, w, plan: Optional[Plan] = None, out=None):
+    _dev(pointer, node_idx, edge_idx, x, w, out)
+    n_rows, f = pointer.numel() - 1, _feat(x)
+    heads = _feat(w)
+    if f % heads:
+        raise GphlError("feature width must be a multiple of the number of weight columns")
+    y = out if out is not None else torch.empty((n_rows, f), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib().gphl_spmm_u_mul_e_sum_f32(_h(plan), _ptr(pointer), _ptr(node_idx), _ptr(edge_idx), n_rows, heads,
+                                               f // heads, _ptr(x), _ptr(w), _ptr(y), _stream(x)), "spmm_u_mul_e_sum")
+    return y
+
+
+def sddmm_u_add_v(src, dst, l, r, out=None):
+    _dev(src, dst, l, r, out)
+    e, f = src.numel(), _feat(l)
+    z = out if out is not None else torch.empty((e, f), dtype=torch.float32, device=l.device)
+    fn = lib().gphl_sddmm_u_add_v_f32_i64 if src.dtype == torch.int64 else lib().gphl_sddmm_u_add_v_f32_i32
+    with torch.cuda.device(l.device):
+        _check(fn(_ptr(src), _ptr(dst), e, f, _ptr(l), _ptr(r), _ptr(z), _stream(l)), "sddmm_u_add_v")
+    return z
+
+
+def sddmm_u_dot_v(src, dst, l, r, heads: int, out=None):
+    _dev(src, dst, l, r, out)
+    e, f = src.numel(), _feat(l)
+    z = out if out is not None else torch.empty((e, heads), dtype=torch.float32, device=l.device)
+    fn = lib().gphl_sddmm_u_dot_v_f32_i64 if src.dtype == torch.int64 else lib().gphl_sddmm_u_dot_v_f32_i32
+    with torch.cuda.device(l.device):
+        _check(fn(_ptr(src), _ptr(dst), e, heads, f // heads, _ptr(l), _ptr(r), _ptr(z), _stream(l)), "sddmm_u_dot_v")
+    return z
+
+
+def segment_softmax(pointer, edge_idx, x, plan: Optional[Plan] = None, out=None, stats=None):
+    _dev(pointer, edge_idx, x, out, stats)
+    n_rows, heads = pointer.numel() - 1, _feat(x)
+    y = out if out is not None else torch.zeros_like(x)
+    if stats is None:
+        stats = torch.empty(max(1, 2 * n_rows * heads), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib().gphl_segment_softmax_f32(_h(plan), _ptr(pointer), _ptr(edge_idx), n_rows, heads, _ptr(x), _ptr(y),
+                                              _ptr(stats), _stream(x)), "segment_softmax")
+    return y
+
+
+def gat_fused(pointer, node_idx, edge_idx, el, er, z, slope: float, plan: Optional[Plan] = None,
+              out=None, alpha_out=None, stats=None):
+    _dev(pointer, node_idx, edge_idx, el, er, z, out, alpha_out, stats)
+    n_rows, heads, f = pointer.numel() - 1, _feat(el), _feat(z)
+    y = out if out is not None else torch.empty((n_rows, f), dtype=z.dtype, device=z.device)
+    if stats is None:
+        stats = torch.empty(max(1, 2 * n_rows * heads), dtype=torch.float32, device=z.device)
+    with torch.cuda.device(z.device):
+        if z.dtype == torch.float32:
+            _check(lib().gphl_gat_fused_f32(_h(plan), _ptr(pointer), _ptr(node_idx), _ptr(edge_idx), n_rows, heads,
+                                            f // heads, _ptr(el), _ptr(er), _ptr(z), float(slope), _ptr(y),
+                                            _ptr(alpha_out), _ptr(stats), _stream(z)), "gat_fused")
+        else:
+            _check(lib().gphl_gat_fused_bf16(_h(plan), _ptr(pointer), _ptr(node_idx), n_rows, heads, f // heads,
+                                             _ptr(el), _ptr(er), _ptr(z), float(slope), _ptr(y), _ptr(stats),
+                                             _stream(z)), "gat_fused_bf16")
+    return y
+
+
+def gather_rows(idx, x, idx2=None, out=None):
+    """y[i] = x[idx[i]] (or x[idx[idx2[i]]]) for any dtype and trailing shape."""
+    _dev(idx, idx2, x, out)
+    n_out = (idx2 if idx2 is not None else idx).numel()
+    row_bytes = _feat(x) * x.element_size()
+    y = out if out is not None else torch.empty((n_out,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    fn = lib().gphl_gather_rows_i64 if idx.dtype == torch.int64 else lib().gphl_gather_rows_i32
+    with torch.cuda.device(x.device):
+        _check(fn(_ptr(idx), _ptr(idx2), n_out, row_bytes, _ptr(x), _ptr(y), _stream(x)), "gather_rows")
+    return y
+
+
+def segment_mm(x, w, type_pointer, gather_idx=None, out=None):
+    _dev(x, w, type_pointer, gather_idx, out)
+    m = gather_idx.numel() if gather_idx is not None else x.shape[0]
+    t, k, n = w.shape
+    if x.shape[1] != k:
+        raise GphlError("inner dimensions differ")
+    y = out if out is not None else torch.empty((m, n), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib().gphl_segment_mm_f32(_ptr(x), _ptr(w), _ptr(type_pointer), t, m, k, n, _ptr(gather_idx), _ptr(y),
+                                         _stream(x)), "segment_mm")
+    return y

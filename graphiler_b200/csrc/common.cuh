@@ -1,0 +1,201 @@
+// Shared device/host helpers of the sm_100a kernel library: error reporting, launch
+// accounting, compensated fp32 arithmetic and the row-split work-item format.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/gphl.h"
+
+namespace gphl {
+
+// ---- host: errors and launch accounting ------------------------------------------------
+
+void set_error(const char *fmt, ...);
+extern std::atomic<int64_t> g_launches;
+
+inline int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  set_error("%s", buf);
+  return code;
+}
+
+// Checks the launch that was just issued (no synchronisation) and counts it.
+inline int launched(const char *what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GPHL_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return GPHL_OK;
+}
+
+#define GPHL_CUDA(call)                                                                   \
+  do {                                                                                    \
+    cudaError_t e_ = (call);                                                              \
+    if (e_ != cudaSuccess)                                                                \
+      return ::gphl::fail(GPHL_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_));        \
+  } while (0)
+
+#define GPHL_REQUIRE(cond, ...)                                                           \
+  do {                                                                                    \
+    if (!(cond)) return ::gphl::fail(GPHL_ERR_INVALID_ARGUMENT, __VA_ARGS__);             \
+  } while (0)
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- work items ------------------------------------------------------------------------
+// One item = one contiguous piece [begin, end) of one row's segment.  slot < 0: the piece
+// is the whole row and its result goes straight to the output; slot >= 0: the row was cut
+// and this piece's partial result goes to scratch slot `slot`.
+struct Item {
+  int32_t row, begin, end, slot;
+};
+
+}  // namespace gphl
+
+struct gphl_plan {
+  int64_t n_rows = 0;
+  int32_t chunk = 0;
+  int64_t n_items = 0;
+  int64_t n_split_rows = 0;
+  int64_t n_pieces = 0;
+  int64_t max_feat = 0;
+  gphl::Item *items = nullptr;      // device, n_items
+  int32_t *split_rows = nullptr;    // device, n_split_rows: row id of each cut row
+  int32_t *split_ptr = nullptr;     // device, n_split_rows + 1: first slot of each cut row
+  float *scratch = nullptr;         // device, 2 * n_pieces * max_feat floats (hi plane, lo plane per slot)
+  int64_t scratch_bytes = 0;
+  bool owns_scratch = true;
+};
+
+namespace gphl {
+
+#ifdef __CUDACC__
+
+constexpr unsigned FULL = 0xffffffffu;
+
+// s + err == a + b exactly (Knuth two-sum; no ordering requirement on |a|, |b|).
+__device__ __forceinline__ void two_sum(float a, float b, float &s, float &err) {
+  s = __fadd_rn(a, b);
+  float bb = __fsub_rn(s, a);
+  err = __fadd_rn(__fsub_rn(a, __fsub_rn(s, bb)), __fsub_rn(b, bb));
+}
+
+// Compensated accumulator: value = hi + lo, lo collects the rounding errors of hi.
+struct Acc {
+  float hi, lo;
+  __device__ __forceinline__ void add(float v) {
+    float s, e;
+    two_sum(hi, v, s, e);
+    hi = s;
+    lo = __fadd_rn(lo, e);
+  }
+  // adds the exact product a*b
+  __device__ __forceinline__ void fma_exact(float a, float b) {
+    float p = __fmul_rn(a, b);
+    float pe = __fmaf_rn(a, b, -p);
+    float s, e;
+    two_sum(hi, p, s, e);
+    hi = s;
+    lo = __fadd_rn(lo, __fadd_rn(e, pe));
+  }
+  __device__ __forceinline__ void merge(float ohi, float olo) {
+    float s, e;
+    two_sum(hi, ohi, s, e);
+    hi = s;
+    lo = __fadd_rn(lo, __fadd_rn(e, olo));
+  }
+  __device__ __forceinline__ float value() const { return __fadd_rn(hi, lo); }
+};
+
+__device__ __forceinline__ float leaky(float v, float slope) { return v >= 0.f ? v : v * slope; }
+
+// Online-softmax pair (running maximum, sum of exp(x - maximum)).
+struct MaxSum {
+  float m, s;
+  __device__ __forceinline__ void init() {
+    m = -INFINITY;
+    s = 0.f;
+  }
+  __device__ __forceinline__ void push(float x) {
+    if (x > m) {
+      s = s * expf(m - x) + 1.f;  // m == -inf: s == 0, exp(-inf) == 0
+      m = x;
+    } else {
+      s += expf(x - m);
+    }
+  }
+  __device__ __forceinline__ void merge(float om, float os) {
+    if (os == 0.f) return;
+    if (s == 0.f) {
+      m = om;
+      s = os;
+      return;
+    }
+    float mm = fmaxf(m, om);
+    s = s * expf(m - mm) + os * expf(om - mm);
+    m = mm;
+  }
+};
+
+// 16-byte vector views of a feature row.
+template <typename T>
+struct VecOf;
+template <>
+struct VecOf<float> {
+  static constexpr int N = 4;
+  __device__ __forceinline__ static void load(const float *p, float (&v)[4]) {
+    float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+    v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+  }
+  __device__ __forceinline__ static void store(float *p, const float (&v)[4]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct VecOf<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ __forceinline__ static void load(const __nv_bfloat16 *p, float (&v)[8]) {
+    uint4 t = __ldg(reinterpret_cast<const uint4 *>(p));
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ __forceinline__ static void store(__nv_bfloat16 *p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t *>(&b);
+    }
+    *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void from_f32(float &d, float v) { d = v; }
+__device__ __forceinline__ void from_f32(__nv_bfloat16 &d, float v) { d = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ Item fetch_item(const Item *items, const int32_t *pointer, int64_t i) {
+  if (items) {
+    int4 t = __ldg(reinterpret_cast<const int4 *>(items) + i);
+    return Item{t.x, t.y, t.z, t.w};
+  }
+  return Item{(int32_t)i, __ldg(pointer + i), __ldg(pointer + i + 1), -1};
+}
+
+#endif  // __CUDACC__
+
+}  // namespace gphl

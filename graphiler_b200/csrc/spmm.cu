@@ -1,0 +1,355 @@
+// Row-gather SpMM family for sm_100a: copy_u_sum / copy_e_sum, u_mul_e_sum (per-head edge
+// weights) and the aggregation half of the fused attention operator.
+//
+// Work decomposition: one warp per work item (a whole row, or one `chunk`-entry piece of a
+// hub row).  A feature row is read as 16-byte vectors; rows narrower than 512 B are read by
+// sub-warp groups so that one warp streams 32/LPR neighbour rows at a time.  Each warp first
+// loads 32 neighbour indices with one coalesced access, (for the weighted modes) stages the
+// 32 x H edge weights in shared memory, then issues U independent 16-byte loads per lane
+// before accumulating, which keeps >= U KB per warp in flight.  Sums are compensated
+// (two-sum) fp32 in a fixed order; pieces of a cut row are combined in ascending order by a
+// second small kernel, so the result does not depend on the split or on the GPU count.
+#include "common.cuh"
+
+namespace gphl {
+
+enum Mode { COPY = 0, MUL_E = 1, GAT = 2 };
+
+struct GatherArgs {
+  const Item *items;
+  int64_t n_items;
+  const int32_t *pointer;
+  const int32_t *idx;    // neighbour row per position (node id, or edge id for copy_e)
+  const int32_t *eidx;   // edge id per position (NULL: position == edge id)
+  const void *x;
+  void *y;
+  const float *w;        // MUL_E: (n_edges, H)
+  const float *el, *er;  // GAT: (n_src, H), (n_rows, H)
+  const float *stats;    // GAT: (n_rows, H, 2) = row maximum, reciprocal of the exp-sum
+  float *alpha_out;      // GAT: optional (n_edges, H)
+  float *scratch;
+  int64_t plane;         // floats per scratch plane row (plan->max_feat)
+  float slope;
+  int32_t F, FV, H, DV;  // columns, 16-byte vectors per row, heads, vectors per head
+};
+
+constexpr int WARPS = 8;
+
+template <typename T, int LPR, int NV, int MODE>
+__global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
+  constexpr int VEC = VecOf<T>::N;
+  constexpr int G = 32 / LPR;              // neighbour rows streamed concurrently by one warp
+  constexpr int U = (NV >= 4) ? 2 : 4;     // unroll: independent rows in flight per group
+  extern __shared__ float smem_w[];        // WARPS x 32 x H staged edge weights
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t item_id = (int64_t)blockIdx.x * WARPS + warp;
+  if (item_id >= a.n_items) return;
+  const Item it = fetch_item(a.items, a.pointer, item_id);
+  const int g = lane / LPR, l = lane % LPR;
+  const int tile0 = blockIdx.y * (LPR * NV);
+
+  int cv[NV];
+  bool cok[NV];
+  int head[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    cv[v] = tile0 + v * LPR + l;
+    cok[v] = cv[v] < a.FV;
+    head[v] = (MODE == COPY || !cok[v]) ? 0 : cv[v] / a.DV;
+  }
+
+  Acc acc[NV][VEC];
+#pragma unroll
+  for (int v = 0; v < NV; ++v)
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[v][k].hi = 0.f, acc[v][k].lo = 0.f;
+
+  const T *x = static_cast<const T *>(a.x);
+  float *wsm = smem_w + (size_t)warp * 32 * a.H;
+
+  for (int base = it.begin; base < it.end; base += 32) {
+    const int n = min(32, it.end - base);
+    int my_idx = 0;
+    if (lane < n) my_idx = __ldg(a.idx + base + lane);
+    if (MODE != COPY) {
+      __syncwarp();
+      if (lane < n) {
+        const int eid = a.eidx ? __ldg(a.eidx + base + lane) : base + lane;
+        if (MODE == MUL_E) {
+          for (int h = 0; h < a.H; ++h) wsm[lane * a.H + h] = __ldg(a.w + (int64_t)eid * a.H + h);
+        } else {
+          for (int h = 0; h < a.H; ++h) {
+            const float2 st = __ldg(reinterpret_cast<const float2 *>(a.stats) + (int64_t)it.row * a.H + h);
+            float e = leaky(__ldg(a.el + (int64_t)my_idx * a.H + h) + __ldg(a.er + (int64_t)it.row * a.H + h), a.slope);
+            float wgt = expf(e - st.x) * st.y;
+            wsm[lane * a.H + h] = wgt;
+            if (a.alpha_out && blockIdx.y == 0) a.alpha_out[(int64_t)eid * a.H + h] = wgt;
+          }
+        }
+      }
+      __syncwarp();
+    }
+#pragma unroll 1
+    for (int jj = 0; jj < n; jj += G * U) {
+      float val[U][NV][VEC];
+      int e[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        e[u] = jj + u * G + g;
+        const bool ok = e[u] < n;
+        const int src = __shfl_sync(FULL, my_idx, e[u] & 31);
+        const T *row = x + (int64_t)src * a.F;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          if (ok && cok[v]) {
+            VecOf<T>::load(row + (int64_t)cv[v] * VEC, val[u][v]);
+          } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) val[u][v][k] = 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          if (MODE == COPY) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[v][k].add(val[u][v][k]);
+          } else {
+            const float wgt = (e[u] < n) ? wsm[e[u] * a.H + head[v]] : 0.f;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[v][k].fma_exact(val[u][v][k], wgt);
+          }
+        }
+      }
+    }
+  }
+
+  // combine the G sub-warp groups in a fixed order
+#pragma unroll
+  for (int off = LPR; off < 32; off <<= 1) {
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const float ohi = __shfl_xor_sync(FULL, acc[v][k].hi, off);
+        const float olo = __shfl_xor_sync(FULL, acc[v][k].lo, off);
+        // both partners must add in the same order to hold identical values: order by group id
+        if ((lane & off) == 0) {
+          acc[v][k].merge(ohi, olo);
+        } else {
+          Acc t{ohi, olo};
+          t.merge(acc[v][k].hi, acc[v][k].lo);
+          acc[v][k] = t;
+        }
+      }
+  }
+  if (g != 0) return;
+
+  if (it.slot < 0) {
+    T *y = static_cast<T *>(a.y) + (int64_t)it.row * a.F;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (!cok[v]) continue;
+      float o[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) o[k] = acc[v][k].value();
+      VecOf<T>::store(y + (int64_t)cv[v] * VEC, o);
+    }
+  } else {
+    float *hi = a.scratch + (int64_t)(2 * it.slot) * a.plane;
+    float *lo = hi + a.plane;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (!cok[v]) continue;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        hi[cv[v] * VEC + k] = acc[v][k].hi;
+        lo[cv[v] * VEC + k] = acc[v][k].lo;
+      }
+    }
+  }
+}
+
+// Any shape / alignment: one thread per (item, column), serial over the piece.
+template <typename T, int MODE>
+__global__ void gather_sum_scalar_kernel(GatherArgs a, int32_t D) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= a.n_items * a.F) return;
+  const int64_t item_id = t / a.F;
+  const int f = (int)(t % a.F);
+  const Item it = fetch_item(a.items, a.pointer, item_id);
+  const int h = (MODE == COPY) ? 0 : f / D;
+  const T *x = static_cast<const T *>(a.x);
+  Acc acc{0.f, 0.f};
+  float m = 0.f, inv = 0.f, erv = 0.f;
+  if (MODE == GAT) {
+    m = a.stats[((int64_t)it.row * a.H + h) * 2];
+    inv = a.stats[((int64_t)it.row * a.H + h) * 2 + 1];
+    erv = a.er[(int64_t)it.row * a.H + h];
+  }
+  for (int i = it.begin; i < it.end; ++i) {
+    const int src = a.idx[i];
+    const float v = to_f32(x[(int64_t)src * a.F + f]);
+    if (MODE == COPY) {
+      acc.add(v);
+    } else {
+      const int eid = a.eidx ? a.eidx[i] : i;
+      float wgt;
+      if (MODE == MUL_E) {
+        wgt = a.w[(int64_t)eid * a.H + h];
+      } else {
+        wgt = expf(leaky(a.el[(int64_t)src * a.H + h] + erv, a.slope) - m) * inv;
+        if (a.alpha_out && f == h * D) a.alpha_out[(int64_t)eid * a.H + h] = wgt;
+      }
+      acc.fma_exact(v, wgt);
+    }
+  }
+  if (it.slot < 0) {
+    from_f32(static_cast<T *>(a.y)[(int64_t)it.row * a.F + f], acc.value());
+  } else {
+    a.scratch[(int64_t)(2 * it.slot) * a.plane + f] = acc.hi;
+    a.scratch[(int64_t)(2 * it.slot + 1) * a.plane + f] = acc.lo;
+  }
+}
+
+// Combines the pieces of every cut row, ascending, one thread per (cut row, column).
+template <typename T>
+__global__ void split_reduce_kernel(const int32_t *split_rows, const int32_t *split_ptr, int64_t n_split,
+                                    const float *scratch, int64_t plane, int32_t F, T *y) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_split * F) return;
+  const int64_t r = t / F;
+  const int f = (int)(t % F);
+  Acc acc{0.f, 0.f};
+  for (int s = split_ptr[r]; s < split_ptr[r + 1]; ++s)
+    acc.merge(scratch[(int64_t)(2 * s) * plane + f], scratch[(int64_t)(2 * s + 1) * plane + f]);
+  from_f32(y[(int64_t)split_rows[r] * F + f], acc.value());
+}
+
+template <typename T, int MODE, int LPR, int NV>
+static int launch_vec(const GatherArgs &a, cudaStream_t stream) {
+  const int tiles = (a.FV + LPR * NV - 1) / (LPR * NV);
+  dim3 grid((unsigned)((a.n_items + WARPS - 1) / WARPS), (unsigned)tiles);
+  const size_t smem = (MODE == COPY) ? 0 : sizeof(float) * WARPS * 32 * a.H;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(gather_sum_kernel<T, LPR, NV, MODE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(GPHL_ERR_CUDA, "gather_sum: shared memory opt-in: %s", cudaGetErrorString(e));
+  }
+  gather_sum_kernel<T, LPR, NV, MODE><<<grid, WARPS * 32, smem, stream>>>(a);
+  return launched("gather_sum_kernel");
+}
+
+template <typename T, int MODE>
+static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t stream) {
+  constexpr int VEC = VecOf<T>::N;
+  if (a.n_items == 0 || a.F == 0) return GPHL_OK;
+  if (plan) {
+    a.items = plan->items;
+    a.n_items = plan->n_items;
+    a.scratch = plan->scratch;
+    a.plane = plan->max_feat;
+    if (plan->n_pieces > 0 && a.F > plan->max_feat)
+      return fail(GPHL_ERR_TOO_LARGE, "feature width %d exceeds the plan's scratch width %lld", a.F,
+                  (long long)plan->max_feat);
+  }
+  const bool vec_ok = (a.F % VEC == 0) && aligned16(a.x) && aligned16(a.y) && (MODE == COPY || D % VEC == 0) &&
+                      (MODE == COPY || a.H <= 64);
+  int rc;
+  if (vec_ok) {
+    a.FV = a.F / VEC;
+    a.DV = (MODE == COPY) ? a.FV : D / VEC;
+    if (a.FV <= 1) rc = launch_vec<T, MODE, 1, 1>(a, stream);
+    else if (a.FV <= 2) rc = launch_vec<T, MODE, 2, 1>(a, stream);
+    else if (a.FV <= 4) rc = launch_vec<T, MODE, 4, 1>(a, stream);
+    else if (a.FV <= 8) rc = launch_vec<T, MODE, 8, 1>(a, stream);
+    else if (a.FV <= 16) rc = launch_vec<T, MODE, 16, 1>(a, stream);
+    else if (a.FV <= 32) rc = launch_vec<T, MODE, 32, 1>(a, stream);
+    else if (a.FV <= 64) rc = launch_vec<T, MODE, 32, 2>(a, stream);
+    else rc = launch_vec<T, MODE, 32, 4>(a, stream);
+  } else {
+    const int64_t total = a.n_items * a.F;
+    gather_sum_scalar_kernel<T, MODE><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a, D);
+    rc = launched("gather_sum_scalar_kernel");
+  }
+  if (rc != GPHL_OK) return rc;
+  if (plan && plan->n_split_rows > 0) {
+    const int64_t total = plan->n_split_rows * a.F;
+    split_reduce_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+        plan->split_rows, plan->split_ptr, plan->n_split_rows, plan->scratch, plan->max_feat, a.F,
+        static_cast<T *>(a.y));
+    rc = launched("split_reduce_kernel");
+  }
+  return rc;
+}
+
+static int check_common(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx, int64_t n_rows, int64_t feat,
+                        const void *x, const void *y) {
+  GPHL_REQUIRE(n_rows >= 0 && feat >= 0, "negative size");
+  GPHL_REQUIRE(n_rows < INT32_MAX && feat < (1 << 20), "row count or feature width out of range");
+  if (n_rows == 0 || feat == 0) return GPHL_OK;
+  GPHL_REQUIRE(pointer && idx && x && y, "null pointer argument");
+  GPHL_REQUIRE(!plan || plan->n_rows == n_rows, "plan was built for a different row count");
+  return GPHL_OK;
+}
+
+}  // namespace gphl
+
+using namespace gphl;
+
+extern "C" int gphl_spmm_gather_sum_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx, int64_t n_rows,
+                                        int64_t feat, const float *x, float *y, void *stream) {
+  int rc = check_common(plan, pointer, idx, n_rows, feat, x, y);
+  if (rc != GPHL_OK) return rc;
+  GatherArgs a{};
+  a.n_items = n_rows, a.pointer = pointer, a.idx = idx, a.x = x, a.y = y, a.F = (int32_t)feat, a.H = 1;
+  return dispatch<float, COPY>(plan, a, (int32_t)feat, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int gphl_spmm_gather_sum_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx, int64_t n_rows,
+                                         int64_t feat, const void *x, void *y, void *stream) {
+  int rc = check_common(plan, pointer, idx, n_rows, feat, x, y);
+  if (rc != GPHL_OK) return rc;
+  GatherArgs a{};
+  a.n_items = n_rows, a.pointer = pointer, a.idx = idx, a.x = x, a.y = y, a.F = (int32_t)feat, a.H = 1;
+  return dispatch<__nv_bfloat16, COPY>(plan, a, (int32_t)feat, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int gphl_spmm_u_mul_e_sum_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                                         const int32_t *edge_idx, int64_t n_rows, int64_t heads, int64_t dim,
+                                         const float *x, const float *w, float *y, void *stream) {
+  GPHL_REQUIRE(heads >= 1 && dim >= 1, "heads and dim must be >= 1");
+  int rc = check_common(plan, pointer, node_idx, n_rows, heads * dim, x, y);
+  if (rc != GPHL_OK) return rc;
+  if (n_rows == 0) return GPHL_OK;
+  GPHL_REQUIRE(w != nullptr, "null weight pointer");
+  GatherArgs a{};
+  a.n_items = n_rows, a.pointer = pointer, a.idx = node_idx, a.eidx = edge_idx, a.x = x, a.y = y, a.w = w;
+  a.F = (int32_t)(heads * dim), a.H = (int32_t)heads;
+  return dispatch<float, MUL_E>(plan, a, (int32_t)dim, static_cast<cudaStream_t>(stream));
+}
+
+// Aggregation half of the fused attention operator (the statistics half lives in softmax.cu).
+namespace gphl {
+int gat_aggregate_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx, const int32_t *edge_idx,
+                      int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er, const float *z,
+                      float slope, float *out, float *alpha_out, const float *stats, cudaStream_t stream) {
+  GatherArgs a{};
+  a.n_items = n_rows, a.pointer = pointer, a.idx = node_idx, a.eidx = edge_idx, a.x = z, a.y = out;
+  a.el = el, a.er = er, a.stats = stats, a.alpha_out = alpha_out, a.slope = slope;
+  a.F = (int32_t)(heads * dim), a.H = (int32_t)heads;
+  return dispatch<float, GAT>(plan, a, (int32_t)dim, stream);
+}
+int gat_aggregate_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx, int64_t n_rows,
+                       int64_t heads, int64_t dim, const float *el, const float *er, const void *z, float slope,
+                       void *out, const float *stats, cudaStream_t stream) {
+  GatherArgs a{};
+  a.n_items = n_rows, a.pointer = pointer, a.idx = node_idx, a.x = z, a.y = out;
+  a.el = el, a.er = er, a.stats = stats, a.slope = slope;
+  a.F = (int32_t)(heads * dim), a.H = (int32_t)heads;
+  return dispatch<__nv_bfloat16, GAT>(plan, a, (int32_t)dim, stream);
+}
+}  // namespace gphl

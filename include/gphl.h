@@ -1,0 +1,146 @@
+/*
+ * gphl.h - C ABI of the B200 (sm_100a) sparse message-passing kernel library.
+ *
+ * Every entry point takes plain device pointers and sizes and a CUDA stream (passed as
+ * void*, NULL = the legacy default stream), launches asynchronously on that stream and
+ * returns GPHL_OK or a negative error code; gphl_last_error() gives the message of the
+ * calling thread's last failure.  Nothing here allocates or synchronises unless its comment
+ * says so.  The TorchScript operator library (libgraphiler.so) and the ctypes binding are
+ * thin callers of these functions.
+ *
+ * The reference binds this path through the TorchScript operator registry rather than a C
+ * interface; each entry point names the registered operator / kernel it stands behind.
+ *
+ * Graph arrays follow the reference's DGLGraph layout (include/dglgraph.h:54-74):
+ * `pointer` (n_rows+1) int32, `node_idx` / `edge_idx` (nnz) int32 grouped by row; edge-level
+ * tensors are indexed by edge id.  With the in_* arrays the rows are destinations (CSC,
+ * reduce side); with the out_* arrays they are sources (CSR).
+ *
+ * Floating point: fp32 in/out ("f32") or bf16 storage with fp32 arithmetic ("bf16").  All
+ * reductions use compensated (two-sum) fp32 accumulation in a fixed order, so results are
+ * deterministic and independent of how rows are split or sharded.
+ */
+#ifndef GPHL_H_
+#define GPHL_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GPHL_OK 0
+#define GPHL_ERR_INVALID_ARGUMENT (-1) /* null pointer, negative size, unsupported shape   */
+#define GPHL_ERR_CUDA (-2)             /* a CUDA runtime call or launch failed             */
+#define GPHL_ERR_UNSUPPORTED (-3)      /* shape outside what the kernels cover             */
+#define GPHL_ERR_TOO_LARGE (-4)        /* exceeds a stated fixed capacity                   */
+
+/* Message of the calling thread's last failed call ("" if none). */
+const char *gphl_last_error(void);
+/* Library version, (major << 16) | minor. */
+int gphl_version(void);
+/* Number of kernel launches issued by this process through the library (monotone). */
+int64_t gphl_launch_count(void);
+
+/* ---- row-split plan ------------------------------------------------------------------
+ * Rows longer than `chunk` entries (hub nodes of power-law graphs) are cut into pieces of
+ * `chunk` entries that different warps process; the pieces of one row are then combined in
+ * ascending order.  The plan depends only on the pointer array and `chunk`, never on the
+ * GPU count.  gphl_plan_create copies the pointer array to the host once (it synchronises
+ * `stream`), allocates the plan's device arrays and its scratch for `max_feat` fp32
+ * columns per piece; gphl_plan_destroy frees them.  Replaces the reference's one thread
+ * (or one warp) per row with a serial neighbour loop (spmm.cu:192-280, spmm.cuh:30-71). */
+typedef struct gphl_plan gphl_plan;
+#define GPHL_DEFAULT_CHUNK 512
+int gphl_plan_create(const int32_t *pointer, int64_t n_rows, int32_t chunk, int64_t max_feat,
+                     void *stream, gphl_plan **out_plan);
+void gphl_plan_destroy(gphl_plan *plan);
+int64_t gphl_plan_num_items(const gphl_plan *plan);      /* work items (rows + extra pieces)   */
+int64_t gphl_plan_num_split_rows(const gphl_plan *plan); /* rows that were cut                 */
+int64_t gphl_plan_scratch_bytes(const gphl_plan *plan);
+
+/* ---- SpMM: y[v,:] = sum_{i in seg(v)} x[idx[i],:] ------------------------------------
+ * copy_u_sum when idx = in_node_indices (my_ops::SpMMSrc, spmm.cu:375-389) and copy_e_sum
+ * when idx = in_edge_indices (my_ops::SpMMEdge, spmm.cu:359-373); both go to cuSPARSE in
+ * the reference (spmm.cu:57-104).  x is (n_src_rows, feat) row-major, y (n_rows, feat).
+ * `plan` may be NULL (one warp per row, no splitting). */
+int gphl_spmm_gather_sum_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx,
+                             int64_t n_rows, int64_t feat, const float *x, float *y, void *stream);
+int gphl_spmm_gather_sum_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx,
+                              int64_t n_rows, int64_t feat, const void *x, void *y, void *stream);
+
+/* ---- SpMM: y[v,h,:] = sum_i x[node_idx[i],h,:] * w[edge_idx[i],h] ---------------------
+ * my_ops::gspmm_src_mul_e_sum (CSC arrays, spmm.cu:286-320) and my_ops::gspmm_dst_mul_e_sum
+ * (CSR arrays, spmm.cu:322-356); kernels u_mul_e_sum_kernel(_neat) (spmm.cu:192-280), which
+ * cover one head and 64 columns only.  x (n, heads*dim), w (n_edges, heads), y (n_rows,
+ * heads*dim).  edge_idx may be NULL when edge ids equal row-grouped positions. */
+int gphl_spmm_u_mul_e_sum_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                              const int32_t *edge_idx, int64_t n_rows, int64_t heads, int64_t dim,
+                              const float *x, const float *w, float *y, void *stream);
+
+/* ---- SDDMM: z[e,:] = l[src[e],:] + r[dst[e],:] ----------------------------------------
+ * my_ops::gsddmm_u_add_v_mul_alpha (sddmm.cu:118-134; kernel SDDMMCooKernel,
+ * sddmm.cuh:34-71; `alpha` is ignored there and has no counterpart here).  COO arrays in
+ * edge-id order, int64 as the reference stores them, or an int32 copy. */
+int gphl_sddmm_u_add_v_f32_i64(const int64_t *src, const int64_t *dst, int64_t n_edges, int64_t feat,
+                               const float *l, const float *r, float *z, void *stream);
+int gphl_sddmm_u_add_v_f32_i32(const int32_t *src, const int32_t *dst, int64_t n_edges, int64_t feat,
+                               const float *l, const float *r, float *z, void *stream);
+
+/* ---- SDDMM: z[e,h] = sum_d l[src[e],h,d] * r[dst[e],h,d] ------------------------------
+ * u_dot_v: functor binary::Dot (functor.cuh:103-116) with SDDMMCooTreeReduceKernel
+ * (sddmm.cuh:80-120).  The reference registers no operator for it. */
+int gphl_sddmm_u_dot_v_f32_i64(const int64_t *src, const int64_t *dst, int64_t n_edges, int64_t heads,
+                               int64_t dim, const float *l, const float *r, float *z, void *stream);
+int gphl_sddmm_u_dot_v_f32_i32(const int32_t *src, const int32_t *dst, int64_t n_edges, int64_t heads,
+                               int64_t dim, const float *l, const float *r, float *z, void *stream);
+
+/* ---- segment softmax: per row v and head h, softmax over x[edge_idx[seg(v)],h] ---------
+ * my_ops::SegmentSoftmax (segment_softmax.cu:3-24; kernel softmax_v,
+ * segment_softmax_kernel.cu:4-49, one head only; the multi-head kernel there is an empty
+ * stub).  x, y (n_edges, heads) indexed by edge id; y is written at every edge id that
+ * appears in edge_idx.  `stats` is caller scratch of 2*n_rows*heads floats (row maxima and
+ * reciprocal sums).  edge_idx may be NULL when edge ids equal positions. */
+int gphl_segment_softmax_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *edge_idx,
+                             int64_t n_rows, int64_t heads, const float *x, float *y, float *stats,
+                             void *stream);
+
+/* ---- fused attention: SDDMM u_add_v -> leaky-relu -> edge softmax -> u_mul_e_sum --------
+ * out[v,h,:] = sum_i softmax_i(lrelu(el[u_i,h] + er[v,h])) * z[u_i,h,:].  The reference
+ * runs this as gsddmm_u_add_v_mul_alpha, aten::leaky_relu_, SegmentSoftmax and
+ * gspmm_src_mul_e_sum with three (E,H) round trips through memory; here no edge-level
+ * tensor is materialised unless `alpha_out` (n_edges, heads; indexed by edge id through
+ * edge_idx, or by position when edge_idx is NULL) is non-NULL.  `stats`: 2*n_rows*heads
+ * floats of caller scratch. */
+int gphl_gat_fused_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                       const int32_t *edge_idx, int64_t n_rows, int64_t heads, int64_t dim,
+                       const float *el, const float *er, const float *z, float slope, float *out,
+                       float *alpha_out, float *stats, void *stream);
+int gphl_gat_fused_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                        int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er,
+                        const void *z, float slope, void *out, float *stats, void *stream);
+
+/* ---- broadcasts: y[i,:] = x[idx[i],:] (row gather of row_bytes bytes) -------------------
+ * my_ops::BroadcastSrcNode / DstNode / NodeType / EdgeType (broadcast.cu:58-100, ATen
+ * advanced indexing there); the composed SrcNodeType / DstNodeType forms pass idx2 so that
+ * y[i] = x[idx[idx2[i]]] without materialising the intermediate. */
+int gphl_gather_rows_i64(const int64_t *idx, const int64_t *idx2, int64_t n_out, int64_t row_bytes,
+                         const void *x, void *y, void *stream);
+int gphl_gather_rows_i32(const int32_t *idx, const int32_t *idx2, int64_t n_out, int64_t row_bytes,
+                         const void *x, void *y, void *stream);
+
+/* ---- typed linear: y[p_t:p_{t+1},:] = x[p_t:p_{t+1},:] @ w[t] ---------------------------
+ * my_ops::SegmentMMNode / SegmentMMEdge (segment_mm.cu:4-33: a device-to-host copy of the
+ * pointer, one at::mm per type, one concatenation).  x (m, k), w (n_types, k, n), y (m, n),
+ * all row-major fp32; type_pointer (n_types+1) int32 on the device and never read on the
+ * host.  gather_idx (m) may be non-NULL to take row i of the product from x[gather_idx[i]]
+ * (fuses the BroadcastSrcNode that precedes SegmentMMEdge in the reference's RGCN/HGT
+ * graphs). */
+int gphl_segment_mm_f32(const float *x, const float *w, const int32_t *type_pointer, int64_t n_types,
+                        int64_t m, int64_t k, int64_t n, const int64_t *gather_idx, float *y,
+                        void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPHL_H_ */

@@ -1,0 +1,240 @@
+"""Parity of every CUDA kernel, called through the C ABI, with the float64 CPU oracle on the same
+float32 inputs.  Tolerance: |gpu - truth| <= 1e-6 + 1e-5 |truth| element-wise for floating-point
+reductions; bit-exact for gathers, index handling, zero rows and the plain fp32 add of u_add_v."""
+import numpy as np
+import pytest
+import torch
+
+from graphiler_b200 import capi, synthetic
+from graphiler_b200.graph import debug_graph, debug_hetero_graph, prepare_graph
+from oracle import ops_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+RTOL, ATOL = 1e-5, 1e-6
+
+
+def close(got, truth, rtol=RTOL, atol=ATOL):
+    ok, nbad, err = O.within_tolerance(got.float().cpu().numpy(), truth, rtol, atol)
+    assert ok, f"{nbad} elements outside tolerance, max abs err {err:.3e}"
+
+
+def hub_graph(n=300, e=4000, hub_deg=5000, seed=0, empty=True):
+    """Power-law-ish graph: one hub destination far above the split threshold, many short rows, empty rows."""
+    g = torch.Generator().manual_seed(seed)
+    src = torch.randint(0, n, (e,), generator=g)
+    dst = torch.randint(0, n // 2 if empty else n, (e,), generator=g)
+    src = torch.cat([src, torch.randint(0, n, (hub_deg,), generator=g)])
+    dst = torch.cat([dst, torch.full((hub_deg,), 7)])
+    perm = torch.randperm(src.numel(), generator=g)            # edge ids unrelated to position
+    return prepare_graph(src[perm], dst[perm], n)
+
+
+GRAPHS = {
+    "debug": debug_graph,
+    "hub": hub_graph,
+    "hub2": lambda: hub_graph(n=97, e=500, hub_deg=1100, seed=3, empty=False),
+    "empty": lambda: prepare_graph(torch.zeros(0, dtype=torch.int64), torch.zeros(0, dtype=torch.int64), 5),
+}
+
+
+@pytest.fixture(params=list(GRAPHS))
+def graph(request):
+    return GRAPHS[request.param]()
+
+
+@pytest.mark.parametrize("feat", [1, 3, 4, 16, 40, 64, 100, 128, 256, 516])
+@pytest.mark.parametrize("use_plan", [False, True])
+def test_spmm_copy_u_sum(graph, feat, use_plan):
+    g = graph.to(DEV)
+    x = torch.randn(g.num_nodes, feat, device=DEV)
+    plan = capi.Plan(g.in_pointer, feat, chunk=64) if use_plan else None
+    y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan)
+    truth = O.spmm_src(x, graph.in_pointer, graph.in_node_indices)
+    close(y, truth)
+    empty_rows = (graph.in_degrees() == 0).to(DEV)
+    assert (y[empty_rows] == 0).all()
+
+
+def test_spmm_result_independent_of_plan_when_no_row_is_cut():
+    g = hub_graph(hub_deg=100).to(DEV)
+    x = torch.randn(g.num_nodes, 64, device=DEV)
+    a = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, None)
+    b = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, capi.Plan(g.in_pointer, 64, chunk=512))
+    assert torch.equal(a, b)
+    c = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, capi.Plan(g.in_pointer, 64, chunk=512))
+    assert torch.equal(b, c)              # deterministic across runs
+
+
+@pytest.mark.parametrize("feat", [16, 128])
+def test_spmm_copy_e_sum(graph, feat):
+    g = graph.to(DEV)
+    m = torch.randn(g.num_edges, feat, device=DEV)
+    plan = capi.Plan(g.in_pointer, feat, chunk=128)
+    y = capi.spmm_gather_sum(g.in_pointer, g.in_edge_indices, m, plan)
+    close(y, O.spmm_edge(m, graph.in_pointer, graph.in_edge_indices))
+
+
+@pytest.mark.parametrize("feat", [64, 256])
+def test_spmm_copy_u_sum_bf16(graph, feat):
+    g = graph.to(DEV)
+    x = torch.randn(g.num_nodes, feat, device=DEV).bfloat16()
+    plan = capi.Plan(g.in_pointer, feat, chunk=64)
+    y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan)
+    truth = O.spmm_src(x.float(), graph.in_pointer, graph.in_node_indices)    # oracle on the bf16-rounded inputs
+    # fp32-accumulated sum rounded once to bf16: half an ulp = 2^-9 relative
+    close(y, truth, rtol=2.0 ** -8, atol=1e-6)
+
+
+@pytest.mark.parametrize("heads,dim", [(1, 64), (8, 8), (8, 32), (1, 1), (4, 3), (2, 20), (1, 256)])
+@pytest.mark.parametrize("side", ["src", "dst"])
+def test_spmm_u_mul_e_sum(graph, heads, dim, side):
+    g = graph.to(DEV)
+    x = torch.randn(g.num_nodes, heads * dim, device=DEV)
+    w = torch.randn(g.num_edges, heads, device=DEV)
+    if side == "src":
+        arrs = (g.in_pointer, g.in_node_indices, g.in_edge_indices)
+        ref = (graph.in_pointer, graph.in_node_indices, graph.in_edge_indices)
+    else:
+        arrs = (g.out_pointer, g.out_node_indices, g.out_edge_indices)
+        ref = (graph.out_pointer, graph.out_node_indices, graph.out_edge_indices)
+    plan = capi.Plan(arrs[0], heads * dim, chunk=96)
+    y = capi.spmm_u_mul_e_sum(*arrs, x, w, plan)
+    close(y, O.u_mul_e_sum(x, w, *ref))
+
+
+@pytest.mark.parametrize("feat", [1, 8, 6, 64])
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+def test_sddmm_u_add_v(graph, feat, idx_dtype):
+    g = graph.to(DEV)
+    l = torch.randn(g.num_nodes, feat, device=DEV)
+    r = torch.randn(g.num_nodes, feat, device=DEV)
+    z = capi.sddmm_u_add_v(g.COO_src.to(idx_dtype), g.COO_dst.to(idx_dtype), l, r)
+    expect = l.cpu()[graph.COO_src] + r.cpu()[graph.COO_dst]               # one fp32 add: bit-exact
+    assert torch.equal(z.cpu(), expect.reshape(z.shape))
+    close(z, O.sddmm_u_add_v(l, r, graph.COO_src, graph.COO_dst))
+
+
+@pytest.mark.parametrize("heads,dim", [(8, 16), (1, 64), (3, 5), (8, 1)])
+def test_sddmm_u_dot_v(graph, heads, dim):
+    g = graph.to(DEV)
+    l = torch.randn(g.num_nodes, heads * dim, device=DEV)
+    r = torch.randn(g.num_nodes, heads * dim, device=DEV)
+    z = capi.sddmm_u_dot_v(g.COO_src, g.COO_dst, l, r, heads)
+    close(z, O.sddmm_u_dot_v(l, r, graph.COO_src, graph.COO_dst, heads))
+    z32 = capi.sddmm_u_dot_v(g.COO_src.int(), g.COO_dst.int(), l, r, heads)
+    assert torch.equal(z, z32)
+
+
+@pytest.mark.parametrize("heads", [1, 8, 3, 40])
+@pytest.mark.parametrize("use_plan", [False, True])
+def test_segment_softmax(graph, heads, use_plan):
+    g = graph.to(DEV)
+    x = torch.randn(g.num_edges, heads, device=DEV) * 3
+    plan = capi.Plan(g.in_pointer, heads, chunk=64) if use_plan else None
+    y = capi.segment_softmax(g.in_pointer, g.in_edge_indices, x, plan)
+    close(y, O.segment_softmax(x, graph.in_pointer, graph.in_edge_indices))
+
+
+def test_segment_softmax_all_negative_and_huge_logits():
+    graph = hub_graph()
+    g = graph.to(DEV)
+    x = torch.full((g.num_edges, 2), -300.0, device=DEV)
+    x[:, 1] = torch.randn(g.num_edges, device=DEV) * 50 + 500
+    y = capi.segment_softmax(g.in_pointer, g.in_edge_indices, x, capi.Plan(g.in_pointer, 2, chunk=64))
+    assert torch.isfinite(y).all()
+    close(y, O.segment_softmax(x, graph.in_pointer, graph.in_edge_indices))
+
+
+@pytest.mark.parametrize("heads,dim", [(8, 8), (8, 32), (1, 64), (2, 3), (1, 1)])
+@pytest.mark.parametrize("use_plan", [False, True])
+def test_gat_fused(graph, heads, dim, use_plan):
+    g = graph.to(DEV)
+    el = torch.randn(g.num_nodes, heads, device=DEV) * 2
+    er = torch.randn(g.num_nodes, heads, device=DEV) * 2
+    z = torch.randn(g.num_nodes, heads * dim, device=DEV)
+    plan = capi.Plan(g.in_pointer, heads * dim, chunk=64) if use_plan else None
+    alpha = torch.zeros(g.num_edges, heads, device=DEV)
+    out = capi.gat_fused(g.in_pointer, g.in_node_indices, g.in_edge_indices, el, er, z, 0.2, plan, alpha_out=alpha)
+    truth, talpha = O.gat_fused(el, er, z, 0.2, graph.in_pointer, graph.in_node_indices, graph.in_edge_indices,
+                                return_alpha=True)
+    close(out, truth)
+    close(alpha, talpha)
+    # unfused sequence gives the same numbers within the same tolerance
+    e = capi.sddmm_u_add_v(g.COO_src, g.COO_dst, el, er)
+    e = torch.nn.functional.leaky_relu(e, 0.2)
+    a = capi.segment_softmax(g.in_pointer, g.in_edge_indices, e, plan)
+    out2 = capi.spmm_u_mul_e_sum(g.in_pointer, g.in_node_indices, g.in_edge_indices, z, a, plan)
+    close(out2, truth)
+
+
+def test_gat_fused_bf16():
+    graph = hub_graph()
+    g = graph.to(DEV)
+    heads, dim = 8, 32
+    el = torch.randn(g.num_nodes, heads, device=DEV)
+    er = torch.randn(g.num_nodes, heads, device=DEV)
+    z = torch.randn(g.num_nodes, heads * dim, device=DEV).bfloat16()
+    out = capi.gat_fused(g.in_pointer, g.in_node_indices, None, el, er, z, 0.2, capi.Plan(g.in_pointer, heads * dim, 64))
+    truth = O.gat_fused(el, er, z.float(), 0.2, graph.in_pointer, graph.in_node_indices, graph.in_edge_indices)
+    close(out, truth, rtol=2.0 ** -8, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype,shape", [(torch.float32, (16,)), (torch.float32, (3,)), (torch.float32, (4, 8, 8)),
+                                         (torch.int8, (5,)), (torch.float64, (2,)), (torch.bfloat16, (128,)),
+                                         (torch.float32, ())])
+def test_broadcasts_bit_exact(dtype, shape):
+    graph = debug_hetero_graph()
+    g = graph.to(DEV)
+    x = (torch.randn((g.num_nodes,) + shape, device=DEV) * 10).to(dtype)
+    assert torch.equal(capi.gather_rows(g.COO_src, x), x[g.COO_src])
+    assert torch.equal(capi.gather_rows(g.COO_dst.int(), x), x[g.COO_dst])
+    xt = (torch.randn((g.num_ntypes,) + shape, device=DEV) * 10).to(dtype)
+    assert torch.equal(capi.gather_rows(g.ntype_COO, xt), xt[g.ntype_COO])
+    assert torch.equal(capi.gather_rows(g.ntype_COO, xt, idx2=g.COO_src), xt[g.ntype_COO][g.COO_src])
+    xe = (torch.randn((g.num_etypes,) + shape, device=DEV) * 10).to(dtype)
+    assert torch.equal(capi.gather_rows(g.etype_COO, xe), xe[g.etype_COO])
+
+
+@pytest.mark.parametrize("k,n", [(16, 16), (128, 128), (20, 7), (1, 1), (64, 200)])
+def test_segment_mm(k, n):
+    counts = [0, 130, 1, 0, 700, 63, 64, 65]
+    m, t = sum(counts), len(counts)
+    ptr = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32)
+    x = torch.randn(m, k, device=DEV)
+    w = torch.randn(t, k, n, device=DEV) / max(1, k) ** 0.5
+    y = capi.segment_mm(x, w, ptr.to(DEV))
+    close(y, O.segment_mm(x, w, ptr))
+    gi = torch.randint(0, m, (m,), device=DEV)
+    y2 = capi.segment_mm(x, w, ptr.to(DEV), gather_idx=gi)
+    close(y2, O.segment_mm(x.cpu()[gi.cpu()], w, ptr))
+
+
+@pytest.mark.parametrize("name,scale", [("c1", 0.25), ("c2", 0.05), ("c3", 0.05), ("c4", 0.02), ("c5", 0.002)])
+def test_ops_on_config_shaped_graphs(name, scale):
+    wl = synthetic.make(name, scale=scale)
+    graph = wl.graph
+    g = graph.to(DEV)
+    feat = {"c1": 64, "c2": 256, "c3": 16, "c4": 128, "c5": 256}[name]
+    x = torch.randn(g.num_nodes, feat, device=DEV)
+    plan = capi.Plan(g.in_pointer, feat)
+    y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan)
+    close(y, O.spmm_src(x, graph.in_pointer, graph.in_node_indices))
+    heads = 8
+    w = torch.rand(g.num_edges, heads, device=DEV)
+    y = capi.spmm_u_mul_e_sum(g.in_pointer, g.in_node_indices, g.in_edge_indices, x, w, plan)
+    close(y, O.u_mul_e_sum(x, w, graph.in_pointer, graph.in_node_indices, graph.in_edge_indices))
+    a = capi.segment_softmax(g.in_pointer, g.in_edge_indices, w * 5, plan)
+    close(a, O.segment_softmax(w.cpu() * 5, graph.in_pointer, graph.in_edge_indices))
+
+
+def test_argument_errors_are_reported_not_fatal():
+    g = debug_graph().to(DEV)
+    x = torch.randn(3, 8, device=DEV)
+    plan = capi.Plan(g.in_pointer, 8)
+    with pytest.raises(capi.GphlError):
+        capi.spmm_gather_sum(torch.zeros(10, dtype=torch.int32, device=DEV), g.in_node_indices, x, plan)
+    with pytest.raises(capi.GphlError):
+        capi.Plan(g.in_pointer, 8, chunk=33)
+    y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan)           # context still healthy
+    close(y, O.spmm_src(x, g.in_pointer.cpu(), g.in_node_indices.cpu()))
