@@ -79,8 +79,14 @@ def _check(rc: int, what: str):
         raise GphlError(f"{what} failed ({rc}): {lib().gphl_last_error().decode()}")
 
 
-def _ptr(t: Optional[torch.Tensor]):
-    return None if t is None else c_void_p(t.data_ptr())
+def _ptr(t: Optional[torch.Tensor], empty: Optional[torch.Tensor] = None):
+    """Device address of ``t``.  An empty tensor has no storage; where the C ABI wants a non-null
+    array that it will never read (the index arrays of an edgeless graph), ``empty`` lends its address."""
+    if t is None:
+        return None
+    if t.numel() == 0 and empty is not None:
+        return c_void_p(empty.data_ptr())
+    return c_void_p(t.data_ptr())
 
 
 def _stream(t: torch.Tensor):
@@ -164,7 +170,8 @@ def spmm_gather_sum(pointer, idx, x, plan: Optional[Plan] = None, out=None):
     y = out if out is not None else torch.empty((n_rows, f), dtype=x.dtype, device=x.device)
     fn = {torch.float32: lib().gphl_spmm_gather_sum_f32, torch.bfloat16: lib().gphl_spmm_gather_sum_bf16}[x.dtype]
     with torch.cuda.device(x.device):
-        _check(fn(_h(plan), _ptr(pointer), _ptr(idx), n_rows, f, _ptr(x), _ptr(y), _stream(x)), "spmm_gather_sum")
+        _check(fn(_h(plan), _ptr(pointer), _ptr(idx, pointer), n_rows, f, _ptr(x, pointer), _ptr(y), _stream(x)),
+               "spmm_gather_sum")
     return y
 
 
@@ -176,8 +183,9 @@ def spmm_u_mul_e_sum(pointer, node_idx, edge_idx, x, w, plan: Optional[Plan] = N
         raise GphlError("feature width must be a multiple of the number of weight columns")
     y = out if out is not None else torch.empty((n_rows, f), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _check(lib().gphl_spmm_u_mul_e_sum_f32(_h(plan), _ptr(pointer), _ptr(node_idx), _ptr(edge_idx), n_rows, heads,
-                                               f // heads, _ptr(x), _ptr(w), _ptr(y), _stream(x)), "spmm_u_mul_e_sum")
+        _check(lib().gphl_spmm_u_mul_e_sum_f32(_h(plan), _ptr(pointer), _ptr(node_idx, pointer), _ptr(edge_idx, pointer),
+                                               n_rows, heads, f // heads, _ptr(x), _ptr(w, pointer), _ptr(y), _stream(x)),
+               "spmm_u_mul_e_sum")
     return y
 
 
@@ -208,8 +216,8 @@ def segment_softmax(pointer, edge_idx, x, plan: Optional[Plan] = None, out=None,
     if stats is None:
         stats = torch.empty(max(1, 2 * n_rows * heads), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _check(lib().gphl_segment_softmax_f32(_h(plan), _ptr(pointer), _ptr(edge_idx), n_rows, heads, _ptr(x), _ptr(y),
-                                              _ptr(stats), _stream(x)), "segment_softmax")
+        _check(lib().gphl_segment_softmax_f32(_h(plan), _ptr(pointer), _ptr(edge_idx, pointer), n_rows, heads,
+                                              _ptr(x, pointer), _ptr(y, pointer), _ptr(stats), _stream(x)), "segment_softmax")
     return y
 
 
@@ -222,11 +230,11 @@ def gat_fused(pointer, node_idx, edge_idx, el, er, z, slope: float, plan: Option
         stats = torch.empty(max(1, 2 * n_rows * heads), dtype=torch.float32, device=z.device)
     with torch.cuda.device(z.device):
         if z.dtype == torch.float32:
-            _check(lib().gphl_gat_fused_f32(_h(plan), _ptr(pointer), _ptr(node_idx), _ptr(edge_idx), n_rows, heads,
+            _check(lib().gphl_gat_fused_f32(_h(plan), _ptr(pointer), _ptr(node_idx, pointer), _ptr(edge_idx, pointer), n_rows, heads,
                                             f // heads, _ptr(el), _ptr(er), _ptr(z), float(slope), _ptr(y),
                                             _ptr(alpha_out), _ptr(stats), _stream(z)), "gat_fused")
         else:
-            _check(lib().gphl_gat_fused_bf16(_h(plan), _ptr(pointer), _ptr(node_idx), n_rows, heads, f // heads,
+            _check(lib().gphl_gat_fused_bf16(_h(plan), _ptr(pointer), _ptr(node_idx, pointer), n_rows, heads, f // heads,
                                              _ptr(el), _ptr(er), _ptr(z), float(slope), _ptr(y), _ptr(stats),
                                              _stream(z)), "gat_fused_bf16")
     return y

@@ -35,6 +35,11 @@ def _np(x, dtype=None):
     return x if dtype is None else x.astype(dtype, copy=False)
 
 
+def _rows2d(x: np.ndarray) -> np.ndarray:
+    """View as (rows, product of trailing dims); also valid for zero rows."""
+    return x.reshape(x.shape[0], int(np.prod(x.shape[1:], dtype=np.int64)) if x.ndim > 1 else 1)
+
+
 def _segment_sum(vals: np.ndarray, pointer: np.ndarray) -> np.ndarray:
     """out[v] = sum of vals[pointer[v]:pointer[v+1]] in float64; empty segments give zero rows."""
     pointer = _np(pointer, np.int64)
@@ -85,14 +90,14 @@ def broadcast_dst_node_type(x, ntype_COO, COO_dst):
 def spmm_src(x, in_pointer, in_node_indices):
     """copy_u_sum: y[v] = sum_{i in seg_in(v)} x[in_node_indices[i]]  (spmm.cu:375-389)."""
     x = _np(x)
-    x2 = x.reshape(x.shape[0], -1)
+    x2 = _rows2d(x)
     return _segment_sum(x2[_np(in_node_indices, np.int64)], in_pointer)
 
 
 def spmm_edge(m, in_pointer, in_edge_indices):
     """copy_e_sum: y[v] = sum_{i in seg_in(v)} m[in_edge_indices[i]]  (spmm.cu:359-373)."""
     m = _np(m)
-    m2 = m.reshape(m.shape[0], -1)
+    m2 = _rows2d(m)
     return _segment_sum(m2[_np(in_edge_indices, np.int64)], in_pointer)
 
 
@@ -108,7 +113,7 @@ def u_mul_e_sum(x, w, pointer, node_indices, edge_indices):
     w = _np(w)
     n_feat = int(np.prod(x.shape[1:], dtype=np.int64)) if x.ndim > 1 else 1
     x2 = x.reshape(x.shape[0], n_feat).astype(F64)
-    w2 = w.reshape(w.shape[0], -1).astype(F64)
+    w2 = _rows2d(w).astype(F64)
     h = w2.shape[1]
     assert n_feat % h == 0, "feature width must be a multiple of the head count"
     d = n_feat // h
@@ -132,8 +137,8 @@ def sddmm_u_add_v(lhs, rhs, COO_src, COO_dst):
     operator is ignored by the reference (sddmm.cu:116-129)."""
     l = _np(lhs)
     r = _np(rhs)
-    l2 = l.reshape(l.shape[0], -1).astype(F64)
-    r2 = r.reshape(r.shape[0], -1).astype(F64)
+    l2 = _rows2d(l).astype(F64)
+    r2 = _rows2d(r).astype(F64)
     return l2[_np(COO_src, np.int64)] + r2[_np(COO_dst, np.int64)]
 
 
@@ -157,7 +162,7 @@ def segment_softmax(x, in_pointer, in_edge_indices):
     a segment is below about -87).  Edge ids outside every segment keep 0."""
     x = _np(x)
     shape = x.shape
-    x2 = x.reshape(shape[0], -1).astype(F64)
+    x2 = _rows2d(x).astype(F64)
     ptr = _np(in_pointer, np.int64)
     eid = _np(in_edge_indices, np.int64)
     y = np.zeros_like(x2)
@@ -222,7 +227,7 @@ def gat_fused(el, er, z, slope, in_pointer, in_node_indices, in_edge_indices, re
 
 def spmm_src_loops(x, in_pointer, in_node_indices):
     x = _np(x, F64)
-    x = x.reshape(x.shape[0], -1)
+    x = _rows2d(x)
     ptr = _np(in_pointer, np.int64)
     col = _np(in_node_indices, np.int64)
     out = np.zeros((ptr.size - 1, x.shape[1]), dtype=F64)
@@ -234,9 +239,9 @@ def spmm_src_loops(x, in_pointer, in_node_indices):
 
 def u_mul_e_sum_loops(x, w, pointer, node_indices, edge_indices):
     x = _np(x, F64)
-    x = x.reshape(x.shape[0], -1)
+    x = _rows2d(x)
     w = _np(w, F64)
-    w = w.reshape(w.shape[0], -1)
+    w = _rows2d(w)
     h = w.shape[1]
     d = x.shape[1] // h
     ptr = _np(pointer, np.int64)
@@ -253,7 +258,7 @@ def u_mul_e_sum_loops(x, w, pointer, node_indices, edge_indices):
 def segment_softmax_loops(x, in_pointer, in_edge_indices):
     x = _np(x, F64)
     shape = x.shape
-    x = x.reshape(shape[0], -1)
+    x = _rows2d(x)
     ptr = _np(in_pointer, np.int64)
     eid = _np(in_edge_indices, np.int64)
     y = np.zeros_like(x)
