@@ -1,0 +1,420 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse message-passing path on B200.
+
+Headline workload (every N): the scale-sweep configuration, one GCN layer forward
+(256 -> 256, fp32) on a synthetic R-MAT graph with N = 2.4 M nodes and 60 M edges + self-loops:
+``relu(D^-1/2 * SpMM_copy_u_sum(D^-1/2 * (X @ W)))``.  With more than one GPU the layer is
+partitioned by destination rows (edge-balanced), the projection by equal source blocks, with
+one NCCL all-gather of the projected features per step (strong scaling: the graph is fixed).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+                  [--scale S] [--dtype fp32|bf16] [--no-extras]
+
+Prints one JSON line.  ``value`` is the device-timed layer time with inputs resident in HBM;
+``e2e`` copies the step's node features from pinned host memory and the result back inside the
+timed region; ``roofline`` is the dominant kernel (the row-gather SpMM) timed with CUDA events
+on its launch stream inside the timed loop; ``cpu_baseline`` / ``--impl reference`` time the CPU
+restatement of the reference's user-defined-function path on a bounded slice of the same graph.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from graphiler_b200 import synthetic  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0.0)), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons every 200 ms while active."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def env_world():
+    return int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the restated user-defined-function path on a bounded destination-row slice
+
+def cpu_reference_sample(g_cpu, x_cpu, w_cpu, target_edges: int, threads: int):
+    """One GCN layer on the host: the full dense projection plus message/reduce over a slice of
+    destination rows holding about ``target_edges`` in-edges; returns (seconds scaled to the whole
+    graph, description, slice output rows, row range)."""
+    from oracle import udf_oracle as U
+    torch.set_num_threads(threads)
+    n, e = g_cpu.num_nodes, g_cpu.num_edges
+    ptr = g_cpu.in_pointer.to(torch.int64)
+    r0 = n // 3
+    stop = int(torch.searchsorted(ptr, ptr[r0] + min(target_edges, e)).clamp(max=n))
+    r1 = max(r0 + 1, stop)
+    e_slice = int(ptr[r1] - ptr[r0])
+    deg = g_cpu.in_degrees().clamp(min=1).float()
+    norm = deg.pow(-0.5).unsqueeze(1)
+    t0 = time.perf_counter()
+    h = torch.mm(x_cpu, w_cpu)
+    t_mm = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    out = U.update_all(g_cpu, {"h": h, "norm": norm, "norm_dst": norm}, {}, {}, {},
+                       lambda ed: {"m": ed.src["h"] * ed.src["norm"]},
+                       lambda nd: {"h": torch.relu(torch.sum(nd.mailbox["m"], dim=1) * nd.data["norm_dst"])},
+                       rows=range(r0, r1))["h"]
+    t_udf = time.perf_counter() - t0
+    scaled = t_mm + t_udf * (e / max(1, e_slice))
+    desc = (f"full X@W ({n}x{x_cpu.shape[1]}x{w_cpu.shape[1]}) + message/reduce over destination rows "
+            f"[{r0},{r1}) = {e_slice} of {e} edges, message/reduce time scaled by {e / max(1, e_slice):.1f}")
+    return scaled, desc, out, (r0, r1)
+
+
+# ---------------------------------------------------------------------------------------------
+
+def run_reference(args):
+    world, rank, local = env_world()
+    if rank != 0:
+        return 0
+    gen_dev = f"cuda:{local}" if torch.cuda.is_available() else "cpu"
+    wl = synthetic.make_c5(scale=args.scale, device=gen_dev)
+    g_cpu, x_cpu, w_cpu = wl.graph.to("cpu"), wl.feats.cpu(), wl.params["gcn_w"].cpu()
+    del wl
+    threads = os.cpu_count() or 1
+    target = max(1000, int(g_cpu.num_edges * args.cpu_fraction))
+    times, desc = [], ""
+    for i in range(args.warmup + args.steps):
+        t, desc, _, _ = cpu_reference_sample(g_cpu, x_cpu, w_cpu, target, threads)
+        if i >= args.warmup:
+            times.append(t)
+    ms = 1e3 * sum(times) / len(times)
+    line = {"impl": "reference", "metric": "gcn_layer_fwd_ms", "value": ms, "unit": "ms", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(g_cpu, args, 1),
+            "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": desc},
+            "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+    return 0
+
+
+def workload_config(g, args, world):
+    return {"workload": "c5 scale sweep: GCN layer 256->256 fwd, R-MAT(a=.57,b=c=.19) graph, dst-sorted CSR",
+            "nodes": g.num_nodes, "edges_incl_self_loops": g.num_edges, "feat": 256, "scale": args.scale,
+            "storage": args.dtype, "partition": f"dst-rows x{world} (edge-balanced) + all-gather" if world > 1 else "none",
+            "l2": "inputs (2.4 GB features, 0.25 GB indices) exceed the 126 MB L2; no flush between steps"}
+
+
+def time_loop(fn, steps, warmup, sync):
+    for _ in range(warmup):
+        fn()
+    sync()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    sync()
+    return a.elapsed_time(b) / steps
+
+
+def extras_per_config(dev):
+    """Layer times and per-kernel bandwidth for the four model configurations (N = 1 only)."""
+    from graphiler_b200 import capi, layers
+    hbm, _, _ = measured_peaks()
+    out = {}
+
+    def t(fn, iters=50, warm=10):
+        return time_loop(fn, iters, warm, torch.cuda.synchronize)
+
+    # c1 GAT
+    w = synthetic.make_c1(device="cpu").to(dev)
+    pg = layers.PreparedGraph(w.graph)
+    p, hy = w.params, w.hyper
+    g = w.graph
+    n, e, H, D = g.num_nodes, g.num_edges, int(hy["heads"]), int(hy["dim"])
+    F = H * D
+    z, el, er = layers.gat_projections(w.feats, p["fc_weight"], p["attn_src"], p["attn_dst"])
+    plan = pg.plan_in(F)
+    ms_layer = t(lambda: layers.gat_layer(pg, w.feats, p["fc_weight"], p["attn_src"], p["attn_dst"], hy["slope"]))
+    ms_unf = t(lambda: layers.gat_layer(pg, w.feats, p["fc_weight"], p["attn_src"], p["attn_dst"], hy["slope"], fused=False))
+    ms_k = t(lambda: capi.gat_fused(g.in_pointer, g.in_node_indices, pg.in_eid, el, er, z, hy["slope"], plan))
+    b_alg = (n + 1) * 4 + e * 4 + 2 * n * H * 4 + 2 * n * F * 4
+    out["c1_gat"] = {"layer_ms": ms_layer, "layer_ms_unfused_ops": ms_unf, "gat_fused_ms": ms_k,
+                     "gat_fused_gbs": b_alg / ms_k / 1e6, "gat_fused_frac": b_alg / ms_k / 1e6 / hbm,
+                     "nodes": n, "edges": e}
+    # c2 GCN (two layers)
+    w = synthetic.make_c2(device="cpu").to(dev)
+    pg = layers.PreparedGraph(w.graph)
+    g = w.graph
+    nrm = layers.gcn_norms(pg)
+
+    def gcn2():
+        h = layers.gcn_layer(pg, w.feats, w.params["w1"], nrm, nrm)
+        return layers.gcn_layer(pg, h, w.params["w2"], nrm, nrm, relu=False)
+    ms_model = t(gcn2)
+    h1 = torch.mm(w.feats, w.params["w1"])
+    ms_k = t(lambda: capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, h1, pg.plan_in(256)))
+    b_alg = (g.num_nodes + 1) * 4 + g.num_edges * 4 + 2 * g.num_nodes * 256 * 4
+    out["c2_gcn"] = {"two_layer_ms": ms_model, "layer_ms": ms_model / 2, "spmm_f256_ms": ms_k,
+                     "spmm_f256_gbs": b_alg / ms_k / 1e6, "spmm_f256_frac": b_alg / ms_k / 1e6 / hbm,
+                     "nodes": g.num_nodes, "edges": g.num_edges}
+    # c3 RGCN (two layers)
+    w = synthetic.make_c3(device="cpu").to(dev)
+    pg = layers.PreparedGraph(w.graph)
+    g = w.graph
+
+    def rgcn2():
+        h = torch.relu(layers.rgcn_layer(pg, w.feats, w.params["w1"], w.edata["norm"]))
+        return layers.rgcn_layer(pg, h, w.params["w2"], w.edata["norm"])
+    ms_model = t(rgcn2)
+    ms_k = t(lambda: capi.segment_mm(w.feats, w.params["w1"], g.etype_pointer, gather_idx=g.COO_src))
+    e = g.num_edges
+    b_alg = e * 16 * 4 * 2 + 50 * 16 * 16 * 4
+    out["c3_rgcn"] = {"two_layer_ms": ms_model, "layer_ms": ms_model / 2, "segment_mm_ms": ms_k,
+                      "segment_mm_gbs": b_alg / ms_k / 1e6, "segment_mm_tflops": 2 * e * 16 * 16 / ms_k / 1e9,
+                      "nodes": g.num_nodes, "edges": e}
+    # c4 HGT (two layers)
+    w = synthetic.make_c4(device="cpu").to(dev)
+    pg = layers.PreparedGraph(w.graph)
+    g, hy = w.graph, w.hyper
+
+    def hgt2():
+        h = layers.hgt_layer(pg, w.feats, w.params, int(hy["heads"]), hy["sqrt_dk"])
+        return layers.hgt_layer(pg, h, w.params, int(hy["heads"]), hy["sqrt_dk"])
+    ms_model = t(hgt2, iters=20, warm=5)
+    k = capi.segment_mm(w.feats, w.params["k_weight"], g.ntype_pointer)
+    ms_k = t(lambda: capi.segment_mm(k, w.params["relation_att"], g.etype_pointer, gather_idx=g.COO_src), iters=20, warm=5)
+    e = g.num_edges
+    b_alg = e * 128 * 4 * 2 + 6 * 128 * 128 * 4
+    out["c4_hgt"] = {"two_layer_ms": ms_model, "layer_ms": ms_model / 2, "segment_mm_edge_ms": ms_k,
+                     "segment_mm_edge_gbs": b_alg / ms_k / 1e6, "segment_mm_edge_tflops": 2 * e * 128 * 128 / ms_k / 1e9,
+                     "nodes": g.num_nodes, "edges": e}
+    return out
+
+
+def run_native(args):
+    from graphiler_b200 import capi
+    from graphiler_b200 import dist as gdist
+    import torch.distributed as dist
+
+    world, rank, local = env_world()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernel library has no CPU path")
+    capi.load_library()                       # fail loudly if the native library is missing
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    wl = synthetic.make_c5(scale=args.scale, device=dev)
+    g, x, w = wl.graph, wl.feats, wl.params["gcn_w"]
+    n, e, feat = g.num_nodes, g.num_edges, x.shape[1]
+    norm = g.in_degrees().clamp(min=1).to(torch.float32).pow(-0.5).unsqueeze(1)
+
+    sl = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, feat, dtype=dtype, rank=rank, world=world)
+    lo, hi = sl.block_range
+    r0, r1 = sl.shard.row0, sl.shard.row1
+    x_blk, nsrc_blk, ndst_loc = x[lo:hi].contiguous(), norm[lo:hi].contiguous(), norm[r0:r1].contiguous()
+    g_cpu = g.to("cpu") if (rank == 0 and world == 1 and not args.no_cpu) else None
+    x_cpu = x.cpu() if g_cpu is not None else None
+    del wl, x
+    torch.cuda.empty_cache()
+
+    # per-launch timing of the dominant kernel, on the stream it is launched on
+    kev = []
+
+    def step():
+        mine = sl.my_block()
+        if mine.dtype == x_blk.dtype:
+            torch.mm(x_blk, w, out=mine[:hi - lo])
+            mine[:hi - lo].mul_(nsrc_blk)
+        else:
+            mine[:hi - lo].copy_(torch.mm(x_blk, w).mul_(nsrc_blk))
+        full = sl.all_gather()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        y = capi.spmm_gather_sum(sl.shard.pointer, sl.shard.node_indices, full, sl.plan)
+        b.record()
+        kev.append((a, b))
+        y.mul_(ndst_loc.to(y.dtype))
+        return torch.relu_(y)
+
+    for _ in range(args.warmup):
+        step()
+    sync()
+    kev.clear()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = capi.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        out = step()
+    ev1.record()
+    sync()
+    launches = capi.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms = ev0.elapsed_time(ev1) / args.steps
+    k_ms = sum(a.elapsed_time(b) for a, b in kev) / len(kev)
+    t = torch.tensor([ms, k_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, k_ms_max = float(t[0]), float(t[1])
+
+    # end to end: node features from pinned host memory every step, result back to the host
+    x_host = x_blk.cpu().pin_memory()
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def e2e_step():
+        x_blk.copy_(x_host, non_blocking=True)
+        y = step()
+        out_host.copy_(y, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_ms = time_loop(e2e_step, e2e_steps, 1, sync)
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t[0])
+
+    hbm, _, peak_kind = measured_peaks()
+    s = 2 if dtype == torch.bfloat16 else 4
+    n_loc, e_loc = sl.shard.num_rows, sl.shard.nnz
+    # algorithmic bytes of copy_u_sum on this rank: pointer + indices + every source row once + output rows
+    b_alg = (n_loc + 1) * 4 + e_loc * 4 + n * feat * s + n_loc * feat * s
+    line = None
+    if rank == 0:
+        line = {"metric": "gcn_layer_fwd_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f32" if dtype == torch.float32 else "bf16 storage, f32 arithmetic",
+                "data": "synthetic", "config": workload_config(g, args, world),
+                "edges_per_s": e / (ms * 1e-3),
+                "roofline": {"bound": "hbm", "kernel": "gather_sum_kernel (copy_u_sum, F=256)", "achieved": b_alg / k_ms_max / 1e6,
+                             "peak": hbm, "peak_kind": peak_kind, "unit": "GB/s", "frac": b_alg / k_ms_max / 1e6 / hbm,
+                             "kernel_ms": k_ms_max, "algorithmic_bytes": b_alg,
+                             "gather_bytes_no_reuse": e_loc * feat * s + n_loc * feat * s + e_loc * 4,
+                             "traffic": None},
+                "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * world,
+                        "d2h_bytes_per_step": n * feat * out.element_size()},
+                "gpu_launches": int(launches), "clocks": clocks}
+        prof = ROOT / "profiles" / "traffic.json"
+        if prof.exists():
+            try:
+                tr = json.loads(prof.read_text()).get(f"copy_u_sum_{args.dtype}")
+                if tr and world == 1:
+                    line["roofline"]["traffic"] = tr["dram_bytes_per_edge"] * e_loc
+            except Exception:
+                pass
+    if g_cpu is not None:
+        threads = os.cpu_count() or 1
+        target = max(1000, int(e * args.cpu_fraction))
+        sec, desc, ref_rows, (c0, c1) = cpu_reference_sample(g_cpu, x_cpu, w.cpu(), target, threads)
+        got = out[c0:c1].float().cpu()
+        err = (got - ref_rows).abs().max().item()
+        line["cpu_baseline"] = {"value": sec * 1e3, "unit": "ms", "cores": threads, "kind": "port", "sample": desc,
+                                "max_abs_diff_vs_gpu_on_sample_rows": err}
+    if rank == 0 and world == 1 and not args.no_extras:
+        del sl, out, x_blk
+        torch.cuda.empty_cache()
+        line["per_config"] = extras_per_config(dev)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (testing only)")
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--cpu-fraction", type=float, default=1.0 / 64, help="share of the edges in the CPU sample")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-config layer timings")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "native":
+        args.warmup = 3
+    return run_reference(args) if args.impl == "reference" else run_native(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,136 @@
+"""Destination-row sharding of a full-graph layer across the GPUs of one node.
+
+The reference is single-GPU (python/graphiler/utils/setup.py:117 lists multiple devices as a
+to-do); this module is new functionality.  One process per GPU:
+
+* every operator on the path is a per-destination computation, so rank p owns a contiguous
+  range of destination rows ``[rows[p], rows[p+1])`` chosen to balance the number of in-edges
+  (not rows: power-law graphs put most edges in few rows);
+* the dense projection is balanced by rows instead: rank p projects the equal-sized block
+  ``[p*B, (p+1)*B)`` of source nodes, and one NCCL all-gather over NVLink assembles the full
+  source-feature matrix in each GPU's own memory; kernels then read local memory only;
+* the row-split plan of a shard depends only on each row's own length, so concatenating the
+  shards' outputs in rank order reproduces the single-GPU result bit for bit.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def edge_balanced_row_ranges(pointer: torch.Tensor, world: int) -> List[int]:
+    """Boundaries r_0=0 <= ... <= r_world=N such that every range holds about nnz/world entries."""
+    n = pointer.numel() - 1
+    nnz = int(pointer[-1])
+    p64 = pointer.to(torch.int64)
+    targets = torch.tensor([nnz * k // world for k in range(1, world)], dtype=torch.int64, device=pointer.device)
+    cuts = torch.searchsorted(p64, targets, right=False).clamp(max=n).tolist() if world > 1 else []
+    bounds = [0] + cuts + [n]
+    for i in range(1, len(bounds)):              # keep monotone if many empty rows collapse cuts
+        bounds[i] = max(bounds[i], bounds[i - 1])
+    return bounds
+
+
+def block_rows(n: int, world: int) -> int:
+    """Rows per rank of the equal-sized source blocks (the last block is padded)."""
+    return (n + world - 1) // world
+
+
+@dataclass
+class RowShard:
+    """The CSC slice of one destination-row range: rebased pointer, global source ids."""
+    row0: int
+    row1: int
+    pointer: torch.Tensor          # (row1-row0+1) int32, starts at 0
+    node_indices: torch.Tensor     # (nnz_local) int32, global source node ids
+    edge0: int                     # first CSC position of the range (positions are global edge slots)
+
+    @property
+    def num_rows(self):
+        return self.row1 - self.row0
+
+    @property
+    def nnz(self):
+        return int(self.node_indices.numel())
+
+
+def shard_rows(in_pointer: torch.Tensor, in_node_indices: torch.Tensor, row0: int, row1: int) -> RowShard:
+    e0, e1 = int(in_pointer[row0]), int(in_pointer[row1])
+    ptr = (in_pointer[row0:row1 + 1] - in_pointer[row0]).contiguous()
+    return RowShard(row0, row1, ptr, in_node_indices[e0:e1].contiguous(), e0)
+
+
+class ShardedLayer:
+    """Per-rank state of one sharded layer: row shard, persistent all-gather buffer, plan.
+
+    ``aggregate`` is the per-shard kernel call ``(shard, gathered_features, plan) -> local output``;
+    it defaults to the CUDA kernels and exists as a parameter so the host logic (partition,
+    all-gather, concatenation) can be exercised on CPU ranks.
+    """
+
+    def __init__(self, in_pointer, in_node_indices, num_nodes: int, feat: int, dtype=torch.float32,
+                 rank: Optional[int] = None, world: Optional[int] = None, group=None, make_plan: bool = True):
+        self.group = group
+        self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
+        self.num_nodes, self.feat = num_nodes, feat
+        self.bounds = edge_balanced_row_ranges(in_pointer, self.world)
+        self.shard = shard_rows(in_pointer, in_node_indices, self.bounds[self.rank], self.bounds[self.rank + 1])
+        self.block = block_rows(num_nodes, self.world)
+        dev = in_pointer.device
+        # persistent (world*block, feat) buffer; rows >= num_nodes are padding that no index refers to
+        self.gathered = torch.zeros((self.world * self.block, feat), dtype=dtype, device=dev)
+        self.plan = None
+        if make_plan and in_pointer.is_cuda:
+            from . import capi
+            self.plan = capi.Plan(self.shard.pointer, feat)
+
+    @property
+    def block_range(self):
+        lo = self.rank * self.block
+        return lo, min(self.num_nodes, lo + self.block)
+
+    def my_block(self) -> torch.Tensor:
+        """View of this rank's slot in the gather buffer: write the projected rows here."""
+        lo = self.rank * self.block
+        return self.gathered[lo:lo + self.block]
+
+    def all_gather(self):
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered, self.my_block(), group=self.group)
+        return self.gathered
+
+    def gather_outputs(self, local_out: torch.Tensor) -> torch.Tensor:
+        """Concatenate every rank's output rows in rank order (testing / export helper)."""
+        if self.world == 1:
+            return local_out
+        sizes = [self.bounds[i + 1] - self.bounds[i] for i in range(self.world)]
+        outs = [torch.empty((s,) + tuple(local_out.shape[1:]), dtype=local_out.dtype, device=local_out.device)
+                for s in sizes]
+        dist.all_gather(outs, local_out.contiguous(), group=self.group)
+        return torch.cat(outs, 0)
+
+
+def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, norm_src_block, norm_dst_local,
+                      relu: bool = True, aggregate: Optional[Callable] = None):
+    """One GCN layer on this rank: project the local source block, all-gather, aggregate the local
+    destination rows.  ``feature_block`` holds rows ``sl.block_range`` of the node features."""
+    lo, hi = sl.block_range
+    mine = sl.my_block()
+    if mine.dtype == feature_block.dtype:
+        torch.mm(feature_block, weight, out=mine[:hi - lo])          # project straight into the gather slot
+        mine[:hi - lo].mul_(norm_src_block)
+    else:                                                             # bf16 storage: fp32 product, one rounding
+        mine[:hi - lo].copy_(torch.mm(feature_block, weight).mul_(norm_src_block))
+    full = sl.all_gather()
+    if aggregate is None:
+        from . import capi
+        y = capi.spmm_gather_sum(sl.shard.pointer, sl.shard.node_indices, full, sl.plan)
+    else:
+        y = aggregate(sl.shard, full)
+    if norm_dst_local is not None:
+        y.mul_(norm_dst_local.to(y.dtype))
+    return torch.relu_(y) if relu else y
