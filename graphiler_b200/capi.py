@@ -17,6 +17,8 @@ LIB_DIR = Path(__file__).resolve().parent / "lib"
 KERNEL_LIB = LIB_DIR / "libgphl.so"
 TORCH_OPS_LIB = LIB_DIR / "libgraphiler.so"
 DEFAULT_CHUNK = 512
+ACCUM_FAST = 1        # GPHL_ACCUM_FAST
+EPILOGUE_RELU = 2     # GPHL_EPILOGUE_RELU
 
 _lib = None
 
@@ -33,6 +35,8 @@ SIGNATURES = {
     "gphl_plan_scratch_bytes": (c_int64, [_P]),
     "gphl_spmm_gather_sum_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_spmm_gather_sum_bf16": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P]),
+    "gphl_spmm_gather_sum_ex_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, c_int32, _P, _P]),
+    "gphl_spmm_gather_sum_ex_bf16": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, c_int32, _P, _P]),
     "gphl_spmm_u_mul_e_sum_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_sddmm_u_add_v_f32_i64": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_sddmm_u_add_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P]),
@@ -41,6 +45,9 @@ SIGNATURES = {
     "gphl_segment_softmax_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_gat_fused_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, _P, _P, _P, _P]),
     "gphl_gat_fused_bf16": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, _P, _P, _P]),
+    "gphl_gat_fused_ex_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, c_int32, _P, _P, _P,
+                                      _P]),
+    "gphl_gat_fused_ex_bf16": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, c_int32, _P, _P, _P]),
     "gphl_gather_rows_i64": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_gather_rows_i32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_segment_mm_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, _P]),
@@ -163,15 +170,20 @@ def _feat(x: torch.Tensor) -> int:
     return f
 
 
-def spmm_gather_sum(pointer, idx, x, plan: Optional[Plan] = None, out=None):
-    """y[v] = sum over the segment of v of x[idx[i]] (SpMMSrc with node indices, SpMMEdge with edge ids)."""
-    _dev(pointer, idx, x, out)
+def spmm_gather_sum(pointer, idx, x, plan: Optional[Plan] = None, out=None, dst_scale=None, relu: bool = False,
+                    fast_accum: bool = False):
+    """y[v] = sum over the segment of v of x[idx[i]] (SpMMSrc with node indices, SpMMEdge with edge ids);
+    optionally followed in the same kernel by ``y[v] *= dst_scale[v]`` and ``max(y, 0)``."""
+    _dev(pointer, idx, x, out, dst_scale)
     n_rows, f = pointer.numel() - 1, _feat(x)
     y = out if out is not None else torch.empty((n_rows, f), dtype=x.dtype, device=x.device)
-    fn = {torch.float32: lib().gphl_spmm_gather_sum_f32, torch.bfloat16: lib().gphl_spmm_gather_sum_bf16}[x.dtype]
+    fn = {torch.float32: lib().gphl_spmm_gather_sum_ex_f32, torch.bfloat16: lib().gphl_spmm_gather_sum_ex_bf16}[x.dtype]
+    flags = (ACCUM_FAST if fast_accum else 0) | (EPILOGUE_RELU if relu else 0)
+    if dst_scale is not None and (dst_scale.dtype != torch.float32 or dst_scale.numel() != n_rows):
+        raise GphlError("dst_scale must hold one float32 per output row")
     with torch.cuda.device(x.device):
-        _check(fn(_h(plan), _ptr(pointer), _ptr(idx, pointer), n_rows, f, _ptr(x, pointer), _ptr(y), _stream(x)),
-               "spmm_gather_sum")
+        _check(fn(_h(plan), _ptr(pointer), _ptr(idx, pointer), n_rows, f, _ptr(x, pointer), _ptr(dst_scale), flags,
+                  _ptr(y), _stream(x)), "spmm_gather_sum")
     return y
 
 
@@ -222,21 +234,22 @@ def segment_softmax(pointer, edge_idx, x, plan: Optional[Plan] = None, out=None,
 
 
 def gat_fused(pointer, node_idx, edge_idx, el, er, z, slope: float, plan: Optional[Plan] = None,
-              out=None, alpha_out=None, stats=None):
+              out=None, alpha_out=None, stats=None, fast_accum: bool = False):
     _dev(pointer, node_idx, edge_idx, el, er, z, out, alpha_out, stats)
     n_rows, heads, f = pointer.numel() - 1, _feat(el), _feat(z)
     y = out if out is not None else torch.empty((n_rows, f), dtype=z.dtype, device=z.device)
     if stats is None:
         stats = torch.empty(max(1, 2 * n_rows * heads), dtype=torch.float32, device=z.device)
+    flags = ACCUM_FAST if fast_accum else 0
     with torch.cuda.device(z.device):
         if z.dtype == torch.float32:
-            _check(lib().gphl_gat_fused_f32(_h(plan), _ptr(pointer), _ptr(node_idx, pointer), _ptr(edge_idx, pointer), n_rows, heads,
-                                            f // heads, _ptr(el), _ptr(er), _ptr(z), float(slope), _ptr(y),
-                                            _ptr(alpha_out), _ptr(stats), _stream(z)), "gat_fused")
+            _check(lib().gphl_gat_fused_ex_f32(_h(plan), _ptr(pointer), _ptr(node_idx, pointer), _ptr(edge_idx, pointer),
+                                               n_rows, heads, f // heads, _ptr(el), _ptr(er), _ptr(z), float(slope),
+                                               flags, _ptr(y), _ptr(alpha_out), _ptr(stats), _stream(z)), "gat_fused")
         else:
-            _check(lib().gphl_gat_fused_bf16(_h(plan), _ptr(pointer), _ptr(node_idx, pointer), n_rows, heads, f // heads,
-                                             _ptr(el), _ptr(er), _ptr(z), float(slope), _ptr(y), _ptr(stats),
-                                             _stream(z)), "gat_fused_bf16")
+            _check(lib().gphl_gat_fused_ex_bf16(_h(plan), _ptr(pointer), _ptr(node_idx, pointer), n_rows, heads,
+                                                f // heads, _ptr(el), _ptr(er), _ptr(z), float(slope), flags, _ptr(y),
+                                                _ptr(stats), _stream(z)), "gat_fused_bf16")
     return y
 
 

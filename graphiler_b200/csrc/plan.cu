@@ -58,6 +58,18 @@ extern "C" int gphl_plan_create(const int32_t *pointer, int64_t n_rows, int32_t 
     }
   }
 
+  // Launch order: longest pieces first (stable counting sort on the piece length), so that the
+  // warps of one block finish together and no long piece is left for the tail of the launch.
+  // Scratch slots were assigned in row order above and do not move.
+  {
+    std::vector<int64_t> start((size_t)chunk + 2, 0);
+    for (const Item &it : items) start[(size_t)(chunk - (it.end - it.begin)) + 1]++;
+    for (size_t i = 1; i < start.size(); ++i) start[i] += start[i - 1];
+    std::vector<Item> sorted(items.size());
+    for (const Item &it : items) sorted[(size_t)start[(size_t)(chunk - (it.end - it.begin))]++] = it;
+    items.swap(sorted);
+  }
+
   gphl_plan *p = new gphl_plan();
   p->n_rows = n_rows;
   p->chunk = chunk;

@@ -12,9 +12,10 @@
 namespace gphl {
 
 int gat_aggregate_f32(const gphl_plan *, const int32_t *, const int32_t *, const int32_t *, int64_t, int64_t, int64_t,
-                      const float *, const float *, const float *, float, float *, float *, const float *, cudaStream_t);
+                      const float *, const float *, const float *, float, float *, float *, const float *, int32_t,
+                      cudaStream_t);
 int gat_aggregate_bf16(const gphl_plan *, const int32_t *, const int32_t *, int64_t, int64_t, int64_t, const float *,
-                       const float *, const void *, float, void *, const float *, cudaStream_t);
+                       const float *, const void *, float, void *, const float *, int32_t, cudaStream_t);
 
 struct StatsArgs {
   const Item *items;
@@ -181,10 +182,11 @@ static int gat_check(const gphl_plan *plan, const int32_t *pointer, const int32_
   return GPHL_OK;
 }
 
-extern "C" int gphl_gat_fused_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
-                                  const int32_t *edge_idx, int64_t n_rows, int64_t heads, int64_t dim, const float *el,
-                                  const float *er, const float *z, float slope, float *out, float *alpha_out,
-                                  float *stats, void *stream_) {
+extern "C" int gphl_gat_fused_ex_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                                     const int32_t *edge_idx, int64_t n_rows, int64_t heads, int64_t dim,
+                                     const float *el, const float *er, const float *z, float slope, int32_t flags,
+                                     float *out, float *alpha_out, float *stats, void *stream_) {
+  GPHL_REQUIRE((flags & ~GPHL_ACCUM_FAST) == 0, "unknown flag bits");
   int rc = gat_check(plan, pointer, node_idx, n_rows, heads, dim, el, er, z, out, stats);
   if (rc != GPHL_OK || n_rows == 0) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -193,12 +195,22 @@ extern "C" int gphl_gat_fused_f32(const gphl_plan *plan, const int32_t *pointer,
   rc = run_stats<true>(plan, a, n_rows, stream);
   if (rc != GPHL_OK) return rc;
   return gat_aggregate_f32(plan, pointer, node_idx, edge_idx, n_rows, heads, dim, el, er, z, slope, out, alpha_out,
-                           stats, stream);
+                           stats, flags, stream);
 }
 
-extern "C" int gphl_gat_fused_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
-                                   int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er,
-                                   const void *z, float slope, void *out, float *stats, void *stream_) {
+extern "C" int gphl_gat_fused_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                                  const int32_t *edge_idx, int64_t n_rows, int64_t heads, int64_t dim, const float *el,
+                                  const float *er, const float *z, float slope, float *out, float *alpha_out,
+                                  float *stats, void *stream) {
+  return gphl_gat_fused_ex_f32(plan, pointer, node_idx, edge_idx, n_rows, heads, dim, el, er, z, slope, 0, out,
+                               alpha_out, stats, stream);
+}
+
+extern "C" int gphl_gat_fused_ex_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                                      int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er,
+                                      const void *z, float slope, int32_t flags, void *out, float *stats,
+                                      void *stream_) {
+  GPHL_REQUIRE((flags & ~GPHL_ACCUM_FAST) == 0, "unknown flag bits");
   int rc = gat_check(plan, pointer, node_idx, n_rows, heads, dim, el, er, z, out, stats);
   if (rc != GPHL_OK || n_rows == 0) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -206,5 +218,11 @@ extern "C" int gphl_gat_fused_bf16(const gphl_plan *plan, const int32_t *pointer
   a.pointer = pointer, a.idx = node_idx, a.el = el, a.er = er, a.slope = slope, a.stats = stats, a.H = (int32_t)heads;
   rc = run_stats<true>(plan, a, n_rows, stream);
   if (rc != GPHL_OK) return rc;
-  return gat_aggregate_bf16(plan, pointer, node_idx, n_rows, heads, dim, el, er, z, slope, out, stats, stream);
+  return gat_aggregate_bf16(plan, pointer, node_idx, n_rows, heads, dim, el, er, z, slope, out, stats, flags, stream);
+}
+
+extern "C" int gphl_gat_fused_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                                   int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er,
+                                   const void *z, float slope, void *out, float *stats, void *stream) {
+  return gphl_gat_fused_ex_bf16(plan, pointer, node_idx, n_rows, heads, dim, el, er, z, slope, 0, out, stats, stream);
 }

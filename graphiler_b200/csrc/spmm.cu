@@ -29,13 +29,50 @@ struct GatherArgs {
   float *alpha_out;      // GAT: optional (n_edges, H)
   float *scratch;
   int64_t plane;         // floats per scratch plane row (plan->max_feat)
+  const float *dst_scale;  // optional per-row factor applied to the finished sum (epilogue)
   float slope;
+  int32_t relu;          // epilogue: max(., 0)
+  int32_t exact;         // 1: compensated accumulation (default), 0: plain fp32 adds
   int32_t F, FV, H, DV;  // columns, 16-byte vectors per row, heads, vectors per head
 };
 
 constexpr int WARPS = 8;
 
-template <typename T, int LPR, int NV, int MODE>
+// Raw 16-byte vector of a row; elements are widened to fp32 only when they are accumulated, so
+// loads in flight cost four registers each whatever the storage type.
+template <typename T>
+__device__ __forceinline__ void unpack(const uint4 &r, float (&v)[VecOf<T>::N]);
+template <>
+__device__ __forceinline__ void unpack<float>(const uint4 &r, float (&v)[4]) {
+  v[0] = __uint_as_float(r.x), v[1] = __uint_as_float(r.y), v[2] = __uint_as_float(r.z), v[3] = __uint_as_float(r.w);
+}
+template <>
+__device__ __forceinline__ void unpack<__nv_bfloat16>(const uint4 &r, float (&v)[8]) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+// EXACT: compensated (two-sum) accumulation, the default contract of the library.  !EXACT: plain
+// fp32 adds (opt-in; the same arithmetic as the reference's kernels, a third of the instructions).
+template <bool EXACT>
+struct AccT;
+template <>
+struct AccT<true> : Acc {};
+template <>
+struct AccT<false> {
+  float hi;
+  static constexpr float lo = 0.f;
+  __device__ __forceinline__ void add(float v) { hi = __fadd_rn(hi, v); }
+  __device__ __forceinline__ void fma_exact(float a, float b) { hi = __fmaf_rn(a, b, hi); }
+  __device__ __forceinline__ void merge(float ohi, float) { hi = __fadd_rn(hi, ohi); }
+  __device__ __forceinline__ float value() const { return hi; }
+};
+
+template <typename T, int LPR, int NV, int MODE, bool EXACT>
 __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   constexpr int VEC = VecOf<T>::N;
   constexpr int G = 32 / LPR;              // neighbour rows streamed concurrently by one warp
@@ -52,26 +89,35 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   int cv[NV];
   bool cok[NV];
   int head[NV];
+  bool cols_full = true;
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     cv[v] = tile0 + v * LPR + l;
     cok[v] = cv[v] < a.FV;
+    cols_full = cols_full && cok[v];
     head[v] = (MODE == COPY || !cok[v]) ? 0 : cv[v] / a.DV;
+    if (!cok[v]) cv[v] = 0;                // keep addresses in range; the value is discarded
   }
+  cols_full = __all_sync(FULL, cols_full);
 
-  Acc acc[NV][VEC];
+  AccT<EXACT> acc[NV][VEC];
 #pragma unroll
   for (int v = 0; v < NV; ++v)
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) acc[v][k].hi = 0.f, acc[v][k].lo = 0.f;
+    for (int k = 0; k < VEC; ++k) {
+      acc[v][k].hi = 0.f;
+      if constexpr (EXACT) acc[v][k].lo = 0.f;
+    }
 
-  const T *x = static_cast<const T *>(a.x);
+  const uint4 *x = static_cast<const uint4 *>(a.x);
   float *wsm = smem_w + (size_t)warp * 32 * a.H;
 
+  int next_idx = 0;
+  if (it.begin + lane < it.end) next_idx = __ldg(a.idx + it.begin + lane);
   for (int base = it.begin; base < it.end; base += 32) {
     const int n = min(32, it.end - base);
-    int my_idx = 0;
-    if (lane < n) my_idx = __ldg(a.idx + base + lane);
+    const int my_idx = next_idx;
+    if (base + 32 + lane < it.end) next_idx = __ldg(a.idx + base + 32 + lane);   // prefetch the next batch
     if (MODE != COPY) {
       __syncwarp();
       if (lane < n) {
@@ -92,35 +138,42 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
     }
 #pragma unroll 1
     for (int jj = 0; jj < n; jj += G * U) {
-      float val[U][NV][VEC];
+      uint4 raw[U][NV];
       int e[U];
+      if (jj + G * U <= n && cols_full) {
+        // whole group of G*U neighbours present: no predicates on the loads
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        e[u] = jj + u * G + g;
-        const bool ok = e[u] < n;
-        const int src = __shfl_sync(FULL, my_idx, e[u] & 31);
-        const T *row = x + (int64_t)src * a.F;
+        for (int u = 0; u < U; ++u) {
+          e[u] = jj + u * G + g;
+          const int src = __shfl_sync(FULL, my_idx, e[u]);
+          const uint4 *row = x + (int64_t)src * a.FV;
 #pragma unroll
-        for (int v = 0; v < NV; ++v) {
-          if (ok && cok[v]) {
-            VecOf<T>::load(row + (int64_t)cv[v] * VEC, val[u][v]);
-          } else {
+          for (int v = 0; v < NV; ++v) raw[u][v] = __ldg(row + cv[v]);
+        }
+      } else {
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) val[u][v][k] = 0.f;
-          }
+        for (int u = 0; u < U; ++u) {
+          e[u] = jj + u * G + g;
+          const bool ok = e[u] < n;
+          const int src = __shfl_sync(FULL, my_idx, e[u] & 31);
+          const uint4 *row = x + (int64_t)src * a.FV;
+#pragma unroll
+          for (int v = 0; v < NV; ++v) raw[u][v] = (ok && cok[v]) ? __ldg(row + cv[v]) : make_uint4(0, 0, 0, 0);
         }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
+          float val[VEC];
+          unpack<T>(raw[u][v], val);
           if (MODE == COPY) {
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) acc[v][k].add(val[u][v][k]);
+            for (int k = 0; k < VEC; ++k) acc[v][k].add(val[k]);
           } else {
             const float wgt = (e[u] < n) ? wsm[e[u] * a.H + head[v]] : 0.f;
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) acc[v][k].fma_exact(val[u][v][k], wgt);
+            for (int k = 0; k < VEC; ++k) acc[v][k].fma_exact(val[k], wgt);
           }
         }
       }
@@ -135,12 +188,14 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         const float ohi = __shfl_xor_sync(FULL, acc[v][k].hi, off);
-        const float olo = __shfl_xor_sync(FULL, acc[v][k].lo, off);
-        // both partners must add in the same order to hold identical values: order by group id
+        const float olo = EXACT ? __shfl_xor_sync(FULL, (float)acc[v][k].lo, off) : 0.f;
+        // both partners add in the same order (lower group first) and so hold identical values
         if ((lane & off) == 0) {
           acc[v][k].merge(ohi, olo);
         } else {
-          Acc t{ohi, olo};
+          AccT<EXACT> t;
+          t.hi = ohi;
+          if constexpr (EXACT) t.lo = olo;
           t.merge(acc[v][k].hi, acc[v][k].lo);
           acc[v][k] = t;
         }
@@ -150,12 +205,17 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
 
   if (it.slot < 0) {
     T *y = static_cast<T *>(a.y) + (int64_t)it.row * a.F;
+    const float scale = a.dst_scale ? __ldg(a.dst_scale + it.row) : 1.f;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       if (!cok[v]) continue;
       float o[VEC];
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) o[k] = acc[v][k].value();
+      for (int k = 0; k < VEC; ++k) {
+        o[k] = acc[v][k].value();
+        if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
+        if (a.relu) o[k] = fmaxf(o[k], 0.f);
+      }
       VecOf<T>::store(y + (int64_t)cv[v] * VEC, o);
     }
   } else {
@@ -208,7 +268,10 @@ __global__ void gather_sum_scalar_kernel(GatherArgs a, int32_t D) {
     }
   }
   if (it.slot < 0) {
-    from_f32(static_cast<T *>(a.y)[(int64_t)it.row * a.F + f], acc.value());
+    float o = acc.value();
+    if (a.dst_scale) o = __fmul_rn(o, a.dst_scale[it.row]);
+    if (a.relu) o = fmaxf(o, 0.f);
+    from_f32(static_cast<T *>(a.y)[(int64_t)it.row * a.F + f], o);
   } else {
     a.scratch[(int64_t)(2 * it.slot) * a.plane + f] = acc.hi;
     a.scratch[(int64_t)(2 * it.slot + 1) * a.plane + f] = acc.lo;
@@ -218,7 +281,8 @@ __global__ void gather_sum_scalar_kernel(GatherArgs a, int32_t D) {
 // Combines the pieces of every cut row, ascending, one thread per (cut row, column).
 template <typename T>
 __global__ void split_reduce_kernel(const int32_t *split_rows, const int32_t *split_ptr, int64_t n_split,
-                                    const float *scratch, int64_t plane, int32_t F, T *y) {
+                                    const float *scratch, int64_t plane, int32_t F, const float *dst_scale,
+                                    int32_t relu, T *y) {
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_split * F) return;
   const int64_t r = t / F;
@@ -226,21 +290,31 @@ __global__ void split_reduce_kernel(const int32_t *split_rows, const int32_t *sp
   Acc acc{0.f, 0.f};
   for (int s = split_ptr[r]; s < split_ptr[r + 1]; ++s)
     acc.merge(scratch[(int64_t)(2 * s) * plane + f], scratch[(int64_t)(2 * s + 1) * plane + f]);
-  from_f32(y[(int64_t)split_rows[r] * F + f], acc.value());
+  float o = acc.value();
+  if (dst_scale) o = __fmul_rn(o, dst_scale[split_rows[r]]);
+  if (relu) o = fmaxf(o, 0.f);
+  from_f32(y[(int64_t)split_rows[r] * F + f], o);
 }
 
-template <typename T, int MODE, int LPR, int NV>
-static int launch_vec(const GatherArgs &a, cudaStream_t stream) {
+template <typename T, int MODE, int LPR, int NV, bool EXACT>
+static int launch_vec_e(const GatherArgs &a, cudaStream_t stream) {
   const int tiles = (a.FV + LPR * NV - 1) / (LPR * NV);
   dim3 grid((unsigned)((a.n_items + WARPS - 1) / WARPS), (unsigned)tiles);
   const size_t smem = (MODE == COPY) ? 0 : sizeof(float) * WARPS * 32 * a.H;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(gather_sum_kernel<T, LPR, NV, MODE>,
+    cudaError_t e = cudaFuncSetAttribute(gather_sum_kernel<T, LPR, NV, MODE, EXACT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(GPHL_ERR_CUDA, "gather_sum: shared memory opt-in: %s", cudaGetErrorString(e));
   }
-  gather_sum_kernel<T, LPR, NV, MODE><<<grid, WARPS * 32, smem, stream>>>(a);
+  gather_sum_kernel<T, LPR, NV, MODE, EXACT><<<grid, WARPS * 32, smem, stream>>>(a);
   return launched("gather_sum_kernel");
+}
+
+template <typename T, int MODE, int LPR, int NV>
+static int launch_vec(const GatherArgs &a, cudaStream_t stream) {
+  // plain accumulation is offered for the unweighted sum and the fused attention aggregate
+  if (MODE != MUL_E && !a.exact) return launch_vec_e<T, MODE, LPR, NV, false>(a, stream);
+  return launch_vec_e<T, MODE, LPR, NV, true>(a, stream);
 }
 
 template <typename T, int MODE>
@@ -279,8 +353,8 @@ static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t
   if (plan && plan->n_split_rows > 0) {
     const int64_t total = plan->n_split_rows * a.F;
     split_reduce_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        plan->split_rows, plan->split_ptr, plan->n_split_rows, plan->scratch, plan->max_feat, a.F,
-        static_cast<T *>(a.y));
+        plan->split_rows, plan->split_ptr, plan->n_split_rows, plan->scratch, plan->max_feat, a.F, a.dst_scale,
+        a.relu, static_cast<T *>(a.y));
     rc = launched("split_reduce_kernel");
   }
   return rc;
@@ -305,6 +379,7 @@ extern "C" int gphl_spmm_gather_sum_f32(const gphl_plan *plan, const int32_t *po
   int rc = check_common(plan, pointer, idx, n_rows, feat, x, y);
   if (rc != GPHL_OK) return rc;
   GatherArgs a{};
+  a.exact = 1;
   a.n_items = n_rows, a.pointer = pointer, a.idx = idx, a.x = x, a.y = y, a.F = (int32_t)feat, a.H = 1;
   return dispatch<float, COPY>(plan, a, (int32_t)feat, static_cast<cudaStream_t>(stream));
 }
@@ -314,8 +389,35 @@ extern "C" int gphl_spmm_gather_sum_bf16(const gphl_plan *plan, const int32_t *p
   int rc = check_common(plan, pointer, idx, n_rows, feat, x, y);
   if (rc != GPHL_OK) return rc;
   GatherArgs a{};
+  a.exact = 1;
   a.n_items = n_rows, a.pointer = pointer, a.idx = idx, a.x = x, a.y = y, a.F = (int32_t)feat, a.H = 1;
   return dispatch<__nv_bfloat16, COPY>(plan, a, (int32_t)feat, static_cast<cudaStream_t>(stream));
+}
+
+template <typename T>
+static int gather_sum_ex(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx, int64_t n_rows, int64_t feat,
+                         const void *x, const float *dst_scale, int32_t flags, void *y, void *stream) {
+  int rc = check_common(plan, pointer, idx, n_rows, feat, x, y);
+  if (rc != GPHL_OK) return rc;
+  GPHL_REQUIRE((flags & ~(GPHL_ACCUM_FAST | GPHL_EPILOGUE_RELU)) == 0, "unknown flag bits");
+  GatherArgs a{};
+  a.n_items = n_rows, a.pointer = pointer, a.idx = idx, a.x = x, a.y = y, a.F = (int32_t)feat, a.H = 1;
+  a.exact = (flags & GPHL_ACCUM_FAST) ? 0 : 1;
+  a.relu = (flags & GPHL_EPILOGUE_RELU) ? 1 : 0;
+  a.dst_scale = dst_scale;
+  return dispatch<T, COPY>(plan, a, (int32_t)feat, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int gphl_spmm_gather_sum_ex_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx,
+                                           int64_t n_rows, int64_t feat, const float *x, const float *dst_scale,
+                                           int32_t flags, float *y, void *stream) {
+  return gather_sum_ex<float>(plan, pointer, idx, n_rows, feat, x, dst_scale, flags, y, stream);
+}
+
+extern "C" int gphl_spmm_gather_sum_ex_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx,
+                                            int64_t n_rows, int64_t feat, const void *x, const float *dst_scale,
+                                            int32_t flags, void *y, void *stream) {
+  return gather_sum_ex<__nv_bfloat16>(plan, pointer, idx, n_rows, feat, x, dst_scale, flags, y, stream);
 }
 
 extern "C" int gphl_spmm_u_mul_e_sum_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
@@ -327,6 +429,7 @@ extern "C" int gphl_spmm_u_mul_e_sum_f32(const gphl_plan *plan, const int32_t *p
   if (n_rows == 0) return GPHL_OK;
   GPHL_REQUIRE(w != nullptr, "null weight pointer");
   GatherArgs a{};
+  a.exact = 1;
   a.n_items = n_rows, a.pointer = pointer, a.idx = node_idx, a.eidx = edge_idx, a.x = x, a.y = y, a.w = w;
   a.F = (int32_t)(heads * dim), a.H = (int32_t)heads;
   return dispatch<float, MUL_E>(plan, a, (int32_t)dim, static_cast<cudaStream_t>(stream));
@@ -336,8 +439,9 @@ extern "C" int gphl_spmm_u_mul_e_sum_f32(const gphl_plan *plan, const int32_t *p
 namespace gphl {
 int gat_aggregate_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx, const int32_t *edge_idx,
                       int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er, const float *z,
-                      float slope, float *out, float *alpha_out, const float *stats, cudaStream_t stream) {
+                      float slope, float *out, float *alpha_out, const float *stats, int32_t flags, cudaStream_t stream) {
   GatherArgs a{};
+  a.exact = (flags & GPHL_ACCUM_FAST) ? 0 : 1;
   a.n_items = n_rows, a.pointer = pointer, a.idx = node_idx, a.eidx = edge_idx, a.x = z, a.y = out;
   a.el = el, a.er = er, a.stats = stats, a.alpha_out = alpha_out, a.slope = slope;
   a.F = (int32_t)(heads * dim), a.H = (int32_t)heads;
@@ -345,8 +449,9 @@ int gat_aggregate_f32(const gphl_plan *plan, const int32_t *pointer, const int32
 }
 int gat_aggregate_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx, int64_t n_rows,
                        int64_t heads, int64_t dim, const float *el, const float *er, const void *z, float slope,
-                       void *out, const float *stats, cudaStream_t stream) {
+                       void *out, const float *stats, int32_t flags, cudaStream_t stream) {
   GatherArgs a{};
+  a.exact = (flags & GPHL_ACCUM_FAST) ? 0 : 1;
   a.n_items = n_rows, a.pointer = pointer, a.idx = node_idx, a.x = z, a.y = out;
   a.el = el, a.er = er, a.stats = stats, a.slope = slope;
   a.F = (int32_t)(heads * dim), a.H = (int32_t)heads;

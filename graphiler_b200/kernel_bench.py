@@ -1,7 +1,7 @@
 """Per-kernel timing on the benchmark configurations.
 
   python -m graphiler_b200.kernel_bench --config c2 --kernel copy_u_sum [--scale S] [--iters K]
-                                        [--feat F] [--dtype fp32|bf16] [--chunk C]
+                                        [--feat F] [--dtype fp32|bf16] [--chunk C] [--fast]
 
 Times one kernel of the library with CUDA events (warm-up, then K launches) on a seeded synthetic
 graph of the chosen configuration and prints one JSON line with its time, its algorithmic bytes
@@ -22,7 +22,7 @@ KERNELS = ("copy_u_sum", "copy_e_sum", "u_mul_e_sum", "u_add_v", "u_dot_v", "seg
 
 
 def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: int, heads: int, dtype: str,
-        chunk: int, device: str = "cuda:0"):
+        chunk: int, fast: bool = False, device: str = "cuda:0"):
     gen_dev = device if config == "c5" else "cpu"
     wl = synthetic.make(config, scale=scale, device=gen_dev).to(device)
     g = wl.graph
@@ -36,7 +36,7 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
     flops = None
     if kernel == "copy_u_sum":
         plan = pg.plan_in(feat)
-        fn = lambda: capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan)
+        fn = lambda: capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan, fast_accum=fast)
         b_alg = (n + 1) * 4 + e * 4 + 2 * n * feat * s
     elif kernel == "copy_e_sum":
         m = torch.randn(e, feat, generator=gen, device=device)
@@ -69,7 +69,8 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
         er = torch.randn(n, heads, generator=gen, device=device)
         plan = pg.plan_in(feat)
         st = torch.empty(2 * n * heads, device=device)
-        fn = lambda: capi.gat_fused(g.in_pointer, g.in_node_indices, pg.in_eid, el, er, x, 0.2, plan, stats=st)
+        fn = lambda: capi.gat_fused(g.in_pointer, g.in_node_indices, pg.in_eid, el, er, x, 0.2, plan, stats=st,
+                                    fast_accum=fast)
         b_alg = (n + 1) * 4 + e * 4 + 2 * n * heads * 4 + 2 * n * feat * s
     elif kernel == "broadcast_src":
         fn = lambda: capi.gather_rows(g.COO_src, x)
@@ -100,7 +101,7 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / iters
     out = {"config": config, "kernel": kernel, "scale": scale, "nodes": n, "edges": e, "feat": feat, "heads": heads,
-           "dtype": dtype, "chunk": chunk, "ms": ms, "algorithmic_bytes": b_alg, "gbs": b_alg / ms / 1e6,
+           "dtype": dtype, "chunk": chunk, "fast_accum": fast, "ms": ms, "algorithmic_bytes": b_alg, "gbs": b_alg / ms / 1e6,
            "split_rows": pg.plan_in(feat).num_split_rows, "items": pg.plan_in(feat).num_items}
     if flops:
         out["tflops"] = flops / ms / 1e9
@@ -118,8 +119,9 @@ def main():
     ap.add_argument("--heads", type=int, default=8)
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--chunk", type=int, default=capi.DEFAULT_CHUNK)
+    ap.add_argument("--fast", action="store_true", help="plain fp32 accumulation instead of compensated")
     a = ap.parse_args()
-    print(json.dumps(run(a.config, a.kernel, a.scale, a.iters, a.warmup, a.feat, a.heads, a.dtype, a.chunk)))
+    print(json.dumps(run(a.config, a.kernel, a.scale, a.iters, a.warmup, a.feat, a.heads, a.dtype, a.chunk, a.fast)))
 
 
 if __name__ == "__main__":

@@ -69,6 +69,20 @@ int gphl_spmm_gather_sum_f32(const gphl_plan *plan, const int32_t *pointer, cons
 int gphl_spmm_gather_sum_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx,
                               int64_t n_rows, int64_t feat, const void *x, void *y, void *stream);
 
+/* The same sum with options.  dst_scale (n_rows floats, may be NULL) multiplies each finished row
+ * and GPHL_EPILOGUE_RELU clamps it at zero, so that a GCN layer's `relu(norm * sum)`
+ * (examples/GCN/GCN.py:21-27) needs no further pass over the output.  GPHL_ACCUM_FAST replaces the
+ * compensated accumulation by plain fp32 adds (the arithmetic of the reference's kernels): about a
+ * third of the instructions, but individual sums may then miss rtol 1e-5 / atol 1e-6. */
+#define GPHL_ACCUM_FAST 1
+#define GPHL_EPILOGUE_RELU 2
+int gphl_spmm_gather_sum_ex_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx,
+                                int64_t n_rows, int64_t feat, const float *x, const float *dst_scale,
+                                int32_t flags, float *y, void *stream);
+int gphl_spmm_gather_sum_ex_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx,
+                                 int64_t n_rows, int64_t feat, const void *x, const float *dst_scale,
+                                 int32_t flags, void *y, void *stream);
+
 /* ---- SpMM: y[v,h,:] = sum_i x[node_idx[i],h,:] * w[edge_idx[i],h] ---------------------
  * my_ops::gspmm_src_mul_e_sum (CSC arrays, spmm.cu:286-320) and my_ops::gspmm_dst_mul_e_sum
  * (CSR arrays, spmm.cu:322-356); kernels u_mul_e_sum_kernel(_neat) (spmm.cu:192-280), which
@@ -119,6 +133,15 @@ int gphl_gat_fused_f32(const gphl_plan *plan, const int32_t *pointer, const int3
 int gphl_gat_fused_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
                         int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er,
                         const void *z, float slope, void *out, float *stats, void *stream);
+/* The same with `flags` (GPHL_ACCUM_FAST: plain fp32 accumulation of the weighted rows). */
+int gphl_gat_fused_ex_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                          const int32_t *edge_idx, int64_t n_rows, int64_t heads, int64_t dim,
+                          const float *el, const float *er, const float *z, float slope, int32_t flags,
+                          float *out, float *alpha_out, float *stats, void *stream);
+int gphl_gat_fused_ex_bf16(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx,
+                           int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er,
+                           const void *z, float slope, int32_t flags, void *out, float *stats,
+                           void *stream);
 
 /* ---- broadcasts: y[i,:] = x[idx[i],:] (row gather of row_bytes bytes) -------------------
  * my_ops::BroadcastSrcNode / DstNode / NodeType / EdgeType (broadcast.cu:58-100, ATen

@@ -66,6 +66,33 @@ def test_spmm_result_independent_of_plan_when_no_row_is_cut():
     assert torch.equal(b, c)              # deterministic across runs
 
 
+@pytest.mark.parametrize("feat", [4, 64, 256, 30])
+def test_spmm_epilogue_scale_relu(graph, feat):
+    g = graph.to(DEV)
+    x = torch.randn(g.num_nodes, feat, device=DEV)
+    sc = torch.rand(g.num_nodes, device=DEV) + 0.5
+    plan = capi.Plan(g.in_pointer, feat, chunk=64)
+    base = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan)
+    y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan, dst_scale=sc, relu=True)
+    assert torch.equal(y, torch.relu(base * sc.unsqueeze(1)))        # epilogue == the two separate fp32 passes
+    truth = np.maximum(O.spmm_src(x, graph.in_pointer, graph.in_node_indices) * sc.cpu().numpy()[:, None].astype(np.float64), 0)
+    close(y, truth)
+
+
+@pytest.mark.parametrize("feat", [64, 256])
+def test_spmm_fast_accumulation_is_plain_fp32(graph, feat):
+    """GPHL_ACCUM_FAST: plain fp32 adds.  Checked at the accuracy plain fp32 summation has
+    (error relative to the sum of magnitudes), not at the library's default tolerance."""
+    g = graph.to(DEV)
+    x = torch.randn(g.num_nodes, feat, device=DEV)
+    plan = capi.Plan(g.in_pointer, feat, chunk=64)
+    y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan, fast_accum=True)
+    truth = O.spmm_src(x, graph.in_pointer, graph.in_node_indices)
+    mag = O.spmm_src(x.abs(), graph.in_pointer, graph.in_node_indices)
+    err = np.abs(y.cpu().numpy().astype(np.float64) - truth)
+    assert (err <= 1e-6 * (1 + mag)).all()
+
+
 @pytest.mark.parametrize("feat", [16, 128])
 def test_spmm_copy_e_sum(graph, feat):
     g = graph.to(DEV)
