@@ -43,6 +43,7 @@ SIGNATURES = {
     "gphl_sddmm_u_dot_v_f32_i64": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_sddmm_u_dot_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_segment_softmax_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_segment_softmax_noalloc_f32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_gat_fused_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, _P, _P, _P, _P]),
     "gphl_gat_fused_bf16": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, _P, _P, _P]),
     "gphl_gat_fused_ex_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, c_int32, _P, _P, _P,
@@ -231,6 +232,22 @@ def segment_softmax(pointer, edge_idx, x, plan: Optional[Plan] = None, out=None,
         _check(lib().gphl_segment_softmax_f32(_h(plan), _ptr(pointer), _ptr(edge_idx, pointer), n_rows, heads,
                                               _ptr(x, pointer), _ptr(y, pointer), _ptr(stats), _stream(x)), "segment_softmax")
     return y
+
+
+SOFTMAX_NOALLOC_MAX_ROW_HEADS = 1 << 20
+
+
+def segment_softmax_noalloc(pointer, edge_idx, x, out):
+    """Segment softmax through the entry point that allocates nothing: the caller passes the output
+    tensor too, and ``rows * heads`` must not exceed ``SOFTMAX_NOALLOC_MAX_ROW_HEADS``.  For callers
+    that cannot obtain device memory at call time; calls on one device must not overlap."""
+    _dev(pointer, edge_idx, x, out)
+    n_rows, heads = pointer.numel() - 1, _feat(x)
+    with torch.cuda.device(x.device):
+        _check(lib().gphl_segment_softmax_noalloc_f32(_ptr(pointer), _ptr(edge_idx, pointer), n_rows, heads,
+                                                      _ptr(x, pointer), _ptr(out, pointer), _stream(x)),
+               "segment_softmax_noalloc")
+    return out
 
 
 def gat_fused(pointer, node_idx, edge_idx, el, er, z, slope: float, plan: Optional[Plan] = None,

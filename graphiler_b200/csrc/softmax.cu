@@ -7,6 +7,8 @@
 // shuffles.  Pieces of cut rows leave partial pairs in the plan's scratch and a merge
 // kernel combines them in ascending order.  Pass 2 (normalise) writes exp(x - max) / sum at
 // every edge id.  The fused operator replaces pass 2 by the weighted gather in spmm.cu.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace gphl {
@@ -225,4 +227,51 @@ extern "C" int gphl_gat_fused_bf16(const gphl_plan *plan, const int32_t *pointer
                                    int64_t n_rows, int64_t heads, int64_t dim, const float *el, const float *er,
                                    const void *z, float slope, void *out, float *stats, void *stream) {
   return gphl_gat_fused_ex_bf16(plan, pointer, node_idx, n_rows, heads, dim, el, er, z, slope, 0, out, stats, stream);
+}
+
+// ---- segment softmax for callers that must not allocate ---------------------------------------
+//
+// The row statistics (maximum, reciprocal exp-sum per row and head) normally live in scratch the
+// caller hands in.  Some callers have no way to provide device scratch: a host process that gave
+// all device memory to its own pool at start-up and forbids cudaMalloc afterwards (cudaMalloc
+// synchronises the device and its latency is unbounded), or a plugin inside a framework that owns
+// the allocator and offers plugins no allocation hook.  For them the statistics live in the
+// fixed array below, which is part of the library image: every GPU that loads the library holds
+// these 8 MiB until the process exits.
+//
+// In host code `g_softmax_stats` is only a handle for the runtime, not a device address; the
+// address is looked up once per device with cudaGetSymbolAddress and cached.
+static __device__ __align__(256) float g_softmax_stats[2 * GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+float *g_noalloc_stats[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int gphl_segment_softmax_noalloc_f32(const int32_t *pointer, const int32_t *edge_idx, int64_t n_rows,
+                                                int64_t heads, const float *x, float *y, void *stream) {
+  GPHL_REQUIRE(n_rows >= 0 && heads >= 1, "bad sizes");
+  if (n_rows > 0 && (heads > GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS || n_rows > GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS / heads))
+    return fail(GPHL_ERR_TOO_LARGE,
+                "segment_softmax_noalloc: n_rows * heads = %lld exceeds the built-in scratch of %d (row, head) pairs; "
+                "use gphl_segment_softmax_f32 with caller-provided scratch",
+                (long long)(n_rows * heads), GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS);
+  int dev = 0;
+  GPHL_CUDA(cudaGetDevice(&dev));
+  GPHL_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");
+  float *stats = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_stats[dev] == nullptr) {
+      // set-up for this device (it is the current one): resolve the array's device address
+      void *p = nullptr;
+      GPHL_CUDA(cudaGetSymbolAddress(&p, g_softmax_stats));
+      g_noalloc_stats[dev] = static_cast<float *>(p);
+    }
+    stats = g_noalloc_stats[dev];
+  }
+  // Pass 1 writes the pair of every (row, head) that pass 2 reads, so nothing left behind by an
+  // earlier call is ever consumed and the array needs no clearing.
+  return gphl_segment_softmax_f32(nullptr, pointer, edge_idx, n_rows, heads, x, y, stats, stream);
 }

@@ -119,6 +119,23 @@ int gphl_segment_softmax_f32(const gphl_plan *plan, const int32_t *pointer, cons
                              int64_t n_rows, int64_t heads, const float *x, float *y, float *stats,
                              void *stream);
 
+/* Segment softmax that allocates nothing and needs no scratch argument.  No counterpart in the
+ * reference.  It is meant for callers that cannot obtain device memory at call time - a process
+ * that hands the whole GPU to its own pool at start-up and bans cudaMalloc afterwards, or a plugin
+ * whose host framework owns the allocator - and gives the same result as gphl_segment_softmax_f32
+ * with plan = NULL (one warp per row, no row splitting).  The row statistics are kept in an 8 MiB
+ * array inside the library image (held on every GPU that loads the library until exit), which
+ * bounds the problem size: n_rows * heads <= GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS, otherwise
+ * GPHL_ERR_TOO_LARGE is returned and nothing is launched.  The first call on each device looks up
+ * the array's address (cudaGetSymbolAddress) with that device current; make that first call
+ * before any stream capture begins.  It calls no cudaMalloc / cudaFree or allocating library
+ * routine.  All calls on one device share the array: calls whose kernels may overlap on the GPU
+ * (different streams, different host threads) race on it and must be serialised by the caller.
+ * No clearing is needed between calls: every entry that is read was written by the same call. */
+#define GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS (1 << 20)
+int gphl_segment_softmax_noalloc_f32(const int32_t *pointer, const int32_t *edge_idx, int64_t n_rows,
+                                     int64_t heads, const float *x, float *y, void *stream);
+
 /* ---- fused attention: SDDMM u_add_v -> leaky-relu -> edge softmax -> u_mul_e_sum --------
  * out[v,h,:] = sum_i softmax_i(lrelu(el[u_i,h] + er[v,h])) * z[u_i,h,:].  The reference
  * runs this as gsddmm_u_add_v_mul_alpha, aten::leaky_relu_, SegmentSoftmax and

@@ -1,0 +1,79 @@
+"""The allocation-free segment softmax (gphl_segment_softmax_noalloc_f32), called through the C ABI.
+
+Some users of the library cannot get device memory at call time: a serving process that gives the
+whole GPU to its own pool when it starts and forbids cudaMalloc afterwards, or a plugin running
+inside a framework that owns the allocator.  For them this entry point keeps its row statistics in
+a fixed array inside the library instead of caller scratch.  The test checks it against the regular
+entry point (same kernels, caller scratch) bit for bit, on two calls in a row that share the
+built-in array, and checks that a problem beyond the array's capacity is refused with a clear
+message.  The file sorts last so that a run stopping at the first failure has run everything else."""
+import ctypes
+
+import pytest
+import torch
+
+from graphiler_b200 import capi
+from graphiler_b200.graph import debug_graph, prepare_graph
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _graph(n, e, hub, seed):
+    g = torch.Generator().manual_seed(seed)
+    src = torch.cat([torch.randint(0, n, (e,), generator=g), torch.randint(0, n, (hub,), generator=g)])
+    dst = torch.cat([torch.randint(0, n // 2, (e,), generator=g), torch.full((hub,), 3)])
+    perm = torch.randperm(src.numel(), generator=g)
+    return prepare_graph(src[perm], dst[perm], n).to(DEV)
+
+
+def _call_noalloc(lib, g, x, y):
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return lib.gphl_segment_softmax_noalloc_f32(
+        ctypes.c_void_p(g.in_pointer.data_ptr()), ctypes.c_void_p(g.in_edge_indices.data_ptr()),
+        g.num_nodes, x.shape[1], ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), stream)
+
+
+def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row():
+    lib = capi.load_library()
+    cases = [(_graph(4000, 30000, 3000, 0), 8), (debug_graph().to(DEV), 3), (_graph(500, 2000, 700, 1), 1)]
+    for g, heads in cases:                    # later calls reuse the array the earlier ones wrote
+        x = torch.randn(g.num_edges, heads, device=DEV) * 4
+        expect = capi.segment_softmax(g.in_pointer, g.in_edge_indices, x, plan=None)
+        y = torch.zeros_like(x)
+        assert _call_noalloc(lib, g, x, y) == 0, lib.gphl_last_error().decode()
+        torch.cuda.synchronize()
+        assert torch.equal(y, expect)         # same kernels, same order: identical bits (tolerance 0)
+        y2 = torch.zeros_like(x)
+        assert _call_noalloc(lib, g, x, y2) == 0
+        assert torch.equal(y2, expect)
+        # and within the library's tolerance of an independent evaluation
+        ref = torch.zeros_like(x)
+        ptr, eid = g.in_pointer.tolist(), g.in_edge_indices.long()
+        for v in range(min(g.num_nodes, 50)):
+            ids = eid[ptr[v]:ptr[v + 1]]
+            if ids.numel():
+                ref[ids] = torch.softmax(x[ids].double(), 0).float()
+                torch.testing.assert_close(y[ids], ref[ids], rtol=1e-5, atol=1e-6)
+
+
+def test_noalloc_python_wrapper_and_capacity_limit():
+    lib = capi.load_library()
+    g = debug_graph().to(DEV)
+    x = torch.randn(g.num_edges, 2, device=DEV)
+    y = capi.segment_softmax_noalloc(g.in_pointer, g.in_edge_indices, x, torch.empty_like(x))
+    assert torch.equal(y, capi.segment_softmax(g.in_pointer, g.in_edge_indices, x))
+    # one (row, head) pair more than the built-in array holds: refused, nothing launched
+    n_rows = capi.SOFTMAX_NOALLOC_MAX_ROW_HEADS + 1
+    ptr = torch.zeros(n_rows + 1, dtype=torch.int32, device=DEV)
+    before = capi.launch_count()
+    rc = lib.gphl_segment_softmax_noalloc_f32(ctypes.c_void_p(ptr.data_ptr()), ctypes.c_void_p(ptr.data_ptr()), n_rows, 1,
+                                              ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), None)
+    assert rc == -4                                                   # GPHL_ERR_TOO_LARGE
+    msg = lib.gphl_last_error().decode()
+    assert "exceeds" in msg and str(capi.SOFTMAX_NOALLOC_MAX_ROW_HEADS) in msg
+    assert capi.launch_count() == before
+    rc = lib.gphl_segment_softmax_noalloc_f32(ctypes.c_void_p(ptr.data_ptr()), ctypes.c_void_p(ptr.data_ptr()), 1 << 19, 4,
+                                              ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), None)
+    assert rc == -4
+    torch.cuda.synchronize()                                          # the context is still healthy
