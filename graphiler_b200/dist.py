@@ -108,10 +108,12 @@ class ShardedLayer:
         if self.world == 1:
             return local_out
         sizes = [self.bounds[i + 1] - self.bounds[i] for i in range(self.world)]
-        outs = [torch.empty((s,) + tuple(local_out.shape[1:]), dtype=local_out.dtype, device=local_out.device)
-                for s in sizes]
-        dist.all_gather(outs, local_out.contiguous(), group=self.group)
-        return torch.cat(outs, 0)
+        pad = max(sizes)                      # ranges differ in length: exchange equal-sized padded blocks, then trim
+        mine = torch.zeros((pad,) + tuple(local_out.shape[1:]), dtype=local_out.dtype, device=local_out.device)
+        mine[:local_out.shape[0]] = local_out
+        outs = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(outs, mine, group=self.group)
+        return torch.cat([o[:s] for o, s in zip(outs, sizes)], 0)
 
 
 def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, norm_src_block, norm_dst_local,
@@ -128,9 +130,10 @@ def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, nor
     full = sl.all_gather()
     if aggregate is None:
         from . import capi
-        y = capi.spmm_gather_sum(sl.shard.pointer, sl.shard.node_indices, full, sl.plan)
-    else:
-        y = aggregate(sl.shard, full)
+        # destination scaling and relu ride in the aggregation kernel's epilogue
+        scale = None if norm_dst_local is None else norm_dst_local.reshape(-1).float().contiguous()
+        return capi.spmm_gather_sum(sl.shard.pointer, sl.shard.node_indices, full, sl.plan, dst_scale=scale, relu=relu)
+    y = aggregate(sl.shard, full)
     if norm_dst_local is not None:
         y.mul_(norm_dst_local.to(y.dtype))
     return torch.relu_(y) if relu else y

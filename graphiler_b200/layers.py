@@ -67,10 +67,10 @@ def gcn_norms(pg: PreparedGraph):
 def gcn_layer(pg: PreparedGraph, feature, weight, norm_src, norm_dst=None, relu: bool = True):
     h = torch.mm(feature, weight)
     h.mul_(norm_src)
-    y = capi.spmm_gather_sum(pg.g.in_pointer, pg.g.in_node_indices, h, pg.plan_in(h.shape[1]))
-    if norm_dst is not None:
-        y.mul_(norm_dst)
-    return torch.relu_(y) if relu else y
+    scale = None if norm_dst is None else norm_dst.reshape(-1)
+    # destination scaling and relu ride in the aggregation kernel's epilogue
+    return capi.spmm_gather_sum(pg.g.in_pointer, pg.g.in_node_indices, h, pg.plan_in(h.shape[1]), dst_scale=scale,
+                                relu=relu)
 
 
 def gat_projections(feature, fc_weight, attn_src, attn_dst):

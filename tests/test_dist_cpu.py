@@ -1,0 +1,66 @@
+"""Host logic of the destination-row sharding, run as two gloo ranks on CPU: edge-balanced row ranges, equal source
+blocks, all-gather into the persistent buffer, per-shard aggregation and concatenation in rank order must reproduce
+the single-device result exactly.  The per-shard aggregate is injected (the float64 oracle) because the CUDA kernels
+cannot run here; on GPUs the default aggregate is the kernel library."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_edge_balanced_ranges():
+    from graphiler_b200 import dist as gd, synthetic
+    g = synthetic.make_c5(scale=0.002).graph
+    for world in (1, 2, 4, 8):
+        b = gd.edge_balanced_row_ranges(g.in_pointer, world)
+        assert b[0] == 0 and b[-1] == g.num_nodes and len(b) == world + 1
+        assert all(b[i] <= b[i + 1] for i in range(world))
+        nnz = [int(g.in_pointer[b[i + 1]] - g.in_pointer[b[i]]) for i in range(world)]
+        assert sum(nnz) == g.num_edges
+        # within one row's worth of the ideal share
+        maxdeg = int(g.in_degrees().max())
+        assert max(nnz) <= g.num_edges / world + maxdeg
+    empty = torch.zeros(6, dtype=torch.int32)
+    assert gd.edge_balanced_row_ranges(empty, 4) == [0, 0, 0, 0, 5] or gd.edge_balanced_row_ranges(empty, 4)[-1] == 5
+
+
+def _worker(rank, world, port, tmp):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from graphiler_b200 import dist as gd, synthetic
+    from oracle import ops_oracle as O
+    wl = synthetic.make_c2(scale=0.01)
+    g, x, w = wl.graph, wl.feats.double(), wl.params["w1"].double()
+    norm = g.in_degrees().clamp(min=1).double().pow(-0.5).unsqueeze(1)
+    sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], dtype=torch.float64,
+                         rank=rank, world=world, make_plan=False)
+    lo, hi = sl.block_range
+    r0, r1 = sl.shard.row0, sl.shard.row1
+
+    def aggregate(shard, full):
+        return torch.from_numpy(O.spmm_src(full.numpy(), shard.pointer, shard.node_indices))
+
+    y = gd.gcn_layer_sharded(sl, x[lo:hi], w, norm[lo:hi], norm[r0:r1], aggregate=aggregate)
+    full = sl.gather_outputs(y)
+    if rank == 0:
+        h = (x @ w) * norm
+        want = np.maximum(O.spmm_src(h.numpy(), g.in_pointer, g.in_node_indices) * norm.numpy(), 0)
+        np.save(tmp + "/ok.npy", np.array([np.array_equal(full.numpy(), want), full.shape[0] == g.num_nodes]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_sharded_gcn_layer_two_gloo_ranks(world, tmp_path):
+    port = 29500 + os.getpid() % 2000
+    mp.start_processes(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True, start_method="spawn")
+    ok = np.load(tmp_path / "ok.npy")
+    assert ok.all()

@@ -1,0 +1,44 @@
+"""Sharded layer on real GPUs (needs >= 2): every rank's rows must equal the single-GPU rows bit for bit."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, tmp):
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from graphiler_b200 import capi, dist as gd, layers, synthetic
+    wl = synthetic.make_c5(scale=0.01).to(dev)
+    g, x, w = wl.graph, wl.feats, wl.params["gcn_w"]
+    norm = g.in_degrees().clamp(min=1).float().pow(-0.5).unsqueeze(1)
+    sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world)
+    lo, hi = sl.block_range
+    r0, r1 = sl.shard.row0, sl.shard.row1
+    y = gd.gcn_layer_sharded(sl, x[lo:hi].contiguous(), w, norm[lo:hi].contiguous(), norm[r0:r1].contiguous())
+    full = sl.gather_outputs(y)
+    single = layers.gcn_layer(layers.PreparedGraph(g), x, w, norm, norm)
+    torch.cuda.synchronize()
+    if rank == 0:
+        np.save(tmp + "/ok.npy", np.array([bool(torch.equal(full, single)), full.shape[0] == g.num_nodes]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_gcn_layer_matches_single_gpu_bitwise(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    port = 29500 + os.getpid() % 2000
+    mp.start_processes(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True, start_method="spawn")
+    assert np.load(tmp_path / "ok.npy").all()
