@@ -323,11 +323,15 @@ def run_native(args):
         sampler.start()
     launches0 = capi.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.profiler_range:
+        torch.cuda.profiler.start()           # ncu --profile-from-start off captures the timed steps only
     ev0.record()
     for _ in range(args.steps):
         out = step()
     ev1.record()
     sync()
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     launches = capi.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     ms = ev0.elapsed_time(ev1) / args.steps
@@ -412,6 +416,8 @@ def main():
     ap.add_argument("--cpu-fraction", type=float, default=1.0 / 64, help="share of the edges in the CPU sample")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-config layer timings")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--fast-accum", action="store_true",
                     help="plain fp32 accumulation in the SpMM (default: compensated, the library's parity contract)")
     args = ap.parse_args()

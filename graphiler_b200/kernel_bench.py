@@ -94,11 +94,13 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
         fn()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()               # a profiler started with --profile-from-start off sees only these launches
     a.record()
     for _ in range(iters):
         fn()
     b.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     ms = a.elapsed_time(b) / iters
     out = {"config": config, "kernel": kernel, "scale": scale, "nodes": n, "edges": e, "feat": feat, "heads": heads,
            "dtype": dtype, "chunk": chunk, "fast_accum": fast, "ms": ms, "algorithmic_bytes": b_alg, "gbs": b_alg / ms / 1e6,
