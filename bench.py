@@ -260,7 +260,7 @@ def extras_per_config(dev):
 
 
 def run_native(args):
-    from graphiler_b200 import capi
+    from graphiler_b200 import capi, layers
     from graphiler_b200 import dist as gdist
     import torch.distributed as dist
 
@@ -300,11 +300,16 @@ def run_native(args):
 
     def step():
         mine = sl.my_block()
-        if mine.dtype == x_blk.dtype:
-            torch.mm(x_blk, w, out=mine[:hi - lo])
-            mine[:hi - lo].mul_(nsrc_blk)
+        if args.cublas_projection:
+            if mine.dtype == x_blk.dtype:
+                torch.mm(x_blk, w, out=mine[:hi - lo])
+                mine[:hi - lo].mul_(nsrc_blk)
+            else:
+                mine[:hi - lo].copy_(torch.mm(x_blk, w).mul_(nsrc_blk))
+        elif mine.dtype == x_blk.dtype:
+            layers.project(x_blk, w, nsrc_blk, out=mine[:hi - lo])
         else:
-            mine[:hi - lo].copy_(torch.mm(x_blk, w).mul_(nsrc_blk))
+            mine[:hi - lo].copy_(layers.project(x_blk, w, nsrc_blk))
         full = sl.all_gather()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -416,6 +421,8 @@ def main():
     ap.add_argument("--cpu-fraction", type=float, default=1.0 / 64, help="share of the edges in the CPU sample")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-config layer timings")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cublas-projection", action="store_true",
+                    help="dense projection with torch.mm + a scaling pass instead of the library's tensor-core kernel")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--fast-accum", action="store_true",

@@ -52,6 +52,9 @@ SIGNATURES = {
     "gphl_gather_rows_i64": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_gather_rows_i32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_segment_mm_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, _P]),
+    "gphl_segment_mm_tc_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
+    "gphl_segment_mm_tc_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, c_int32, _P, _P, _P]),
+    "gphl_tc_wait_timeouts": (c_int, [POINTER(c_int)]),
 }
 
 
@@ -282,14 +285,56 @@ def gather_rows(idx, x, idx2=None, out=None):
     return y
 
 
-def segment_mm(x, w, type_pointer, gather_idx=None, out=None):
-    _dev(x, w, type_pointer, gather_idx, out)
+def segment_mm(x, w, type_pointer, gather_idx=None, out=None, row_scale=None, relu: bool = False,
+               tensor_cores: Optional[bool] = None, workspace=None):
+    """y[p_t:p_{t+1}] = x[p_t:p_{t+1}] @ w[t] (rows of x optionally taken through ``gather_idx``), optionally followed
+    by a per-row scale and relu.  ``tensor_cores``: None = use the tcgen05 kernel whenever the shape allows
+    (k % 4 == 0), True = require it, False = the exact-fp32 SIMT kernel."""
+    _dev(x, w, type_pointer, gather_idx, out, row_scale, workspace)
     m = gather_idx.numel() if gather_idx is not None else x.shape[0]
     t, k, n = w.shape
     if x.shape[1] != k:
         raise GphlError("inner dimensions differ")
     y = out if out is not None else torch.empty((m, n), dtype=torch.float32, device=x.device)
+    tc_ok = (k % 4 == 0) and x.data_ptr() % 16 == 0 and y.data_ptr() % 16 == 0
+    use_tc = tc_ok if tensor_cores is None else tensor_cores
+    if use_tc and not tc_ok:
+        raise GphlError("the tensor-core kernel needs k % 4 == 0 and 16-byte aligned tensors")
     with torch.cuda.device(x.device):
-        _check(lib().gphl_segment_mm_f32(_ptr(x), _ptr(w), _ptr(type_pointer), t, m, k, n, _ptr(gather_idx), _ptr(y),
-                                         _stream(x)), "segment_mm")
+        if use_tc:
+            need = int(lib().gphl_segment_mm_tc_workspace_bytes(t, k, n))
+            if workspace is None or workspace.numel() * workspace.element_size() < need:
+                workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+            _check(lib().gphl_segment_mm_tc_f32(_ptr(x), _ptr(w), _ptr(type_pointer), t, m, k, n, _ptr(gather_idx),
+                                                _ptr(row_scale), 1 if relu else 0, _ptr(workspace), _ptr(y), _stream(x)),
+                   "segment_mm_tc")
+        else:
+            _check(lib().gphl_segment_mm_f32(_ptr(x), _ptr(w), _ptr(type_pointer), t, m, k, n, _ptr(gather_idx), _ptr(y),
+                                             _stream(x)), "segment_mm")
+            if row_scale is not None:
+                y.mul_(row_scale.reshape(-1, 1))
+            if relu:
+                torch.relu_(y)
     return y
+
+
+_ONE_TYPE = {}
+
+
+def linear(x, w, row_scale=None, relu: bool = False, out=None, workspace=None):
+    """Dense layer ``relu?(row_scale * (x @ w))`` on the tensor cores: the typed linear with a single type covering
+    all rows.  fp32 in / out with fp32-level accuracy (three-way bf16 split, six products)."""
+    key = (x.device, x.shape[0])
+    ptr = _ONE_TYPE.get(key)
+    if ptr is None:
+        if len(_ONE_TYPE) > 64:
+            _ONE_TYPE.clear()
+        ptr = _ONE_TYPE[key] = torch.tensor([0, x.shape[0]], dtype=torch.int32, device=x.device)
+    return segment_mm(x, w.unsqueeze(0) if w.dim() == 2 else w, ptr, out=out, row_scale=row_scale, relu=relu,
+                      tensor_cores=True, workspace=workspace)
+
+
+def tc_wait_timeouts() -> int:
+    c = c_int(0)
+    _check(lib().gphl_tc_wait_timeouts(ctypes.byref(c)), "gphl_tc_wait_timeouts")
+    return int(c.value)

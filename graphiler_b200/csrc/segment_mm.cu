@@ -5,7 +5,8 @@
 // pointer, so the pointer is never copied to the host.  Row tiles never straddle a type
 // boundary.  Optional row gather (x[gather_idx[i]]) fuses the node->edge broadcast that
 // precedes the edge-typed linear.  This file holds the exact-fp32 SIMT path (shared-memory
-// tiled, 4x4 register blocking, plain FMA chains).
+// tiled, 4x4 register blocking, exact-product compensated accumulation); it is the fallback for
+// shapes the tensor-core kernel does not take.
 #include "common.cuh"
 
 namespace gphl {
@@ -21,19 +22,31 @@ __global__ void __launch_bounds__(256) segment_mm_simt_kernel(const float *__res
   __shared__ float Bs[TK][TN + 4];
   __shared__ int s_seg, s_row0, s_rows;
   const int tid = threadIdx.x;
-  if (tid == 0) {
-    int64_t b = blockIdx.x;
-    s_rows = 0;
-    for (int t = 0; t < n_types; ++t) {
-      const int lo = ptr[t], hi = ptr[t + 1];
-      const int64_t nt = (hi - lo + TM - 1) / TM;
-      if (b < nt) {
-        s_seg = t;
-        s_row0 = lo + (int)b * TM;
-        s_rows = min(TM, hi - s_row0);
-        break;
+  if (tid < 32) {
+    // which (type, row tile) is this block?  32 types per step: tile counts, warp prefix sum, one hit
+    const int lane = tid;
+    const int64_t b = blockIdx.x;
+    if (lane == 0) s_rows = 0;
+    __syncwarp();
+    int64_t base = 0;
+    for (int t0 = 0; t0 < n_types; t0 += 32) {
+      const int t = t0 + lane;
+      const int lo = t < n_types ? __ldg(ptr + t) : 0, hi = t < n_types ? __ldg(ptr + t + 1) : lo;
+      const int nt = (hi - lo + TM - 1) / TM;
+      int incl = nt;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(FULL, incl, d);
+        if (lane >= d) incl += v;
       }
-      b -= nt;
+      const bool hit = t < n_types && b >= base + incl - nt && b < base + incl;
+      if (hit) {
+        s_seg = t;
+        s_row0 = lo + (int)(b - (base + incl - nt)) * TM;
+        s_rows = min(TM, hi - s_row0);
+      }
+      if (__any_sync(FULL, hit)) break;
+      base += __shfl_sync(FULL, incl, 31);
     }
   }
   __syncthreads();
@@ -44,11 +57,11 @@ __global__ void __launch_bounds__(256) segment_mm_simt_kernel(const float *__res
   const int tx = tid & 15, ty = tid >> 4;
   const float *wt = w + (int64_t)seg * K * N;
 
-  float acc[4][4];
+  Acc acc[4][4];   // compensated: a plain fp32 chain of a few hundred products misses atol 1e-6 now and then
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < 4; ++j) acc[i][j].hi = 0.f, acc[i][j].lo = 0.f;
 
   for (int k0 = 0; k0 < K; k0 += TK) {
 #pragma unroll
@@ -77,7 +90,7 @@ __global__ void __launch_bounds__(256) segment_mm_simt_kernel(const float *__res
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) acc[i][j].fma_exact(a[i], b[j]);
     }
     __syncthreads();
   }
@@ -88,7 +101,7 @@ __global__ void __launch_bounds__(256) segment_mm_simt_kernel(const float *__res
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int c = n0 + tx * 4 + j;
-      if (c < N) y[(int64_t)(row0 + r) * N + c] = acc[i][j];
+      if (c < N) y[(int64_t)(row0 + r) * N + c] = acc[i][j].value();
     }
   }
 }

@@ -305,10 +305,23 @@ Tensor segment_mm(const Tensor &x, const Tensor &w, const c10::optional<Tensor> 
   Tensor gi;
   if (gather.has_value()) gi = cuda_idx(gather.value(), torch::kInt64, "gather index");
   c10::cuda::CUDAGuard guard(xc.device());
-  check_rc(gphl_segment_mm_f32(xc.data_ptr<float>(), wc.data_ptr<float>(), pc.data_ptr<int32_t>(), n_types, rows,
-                               xc.size(1), wc.size(2), gather.has_value() ? gi.data_ptr<int64_t>() : nullptr,
-                               y.data_ptr<float>(), stream_of(xc)),
-           "gphl_segment_mm_f32");
+  const int64_t k = xc.size(1), n = wc.size(2);
+  const bool tc = (k % 4 == 0) && (reinterpret_cast<uintptr_t>(xc.data_ptr()) % 16 == 0) &&
+                  (reinterpret_cast<uintptr_t>(y.data_ptr()) % 16 == 0);
+  if (tc) {
+    // tensor-core path: the split weights live in a scratch tensor from the caching allocator
+    Tensor ws = torch::empty({std::max<int64_t>(16, gphl_segment_mm_tc_workspace_bytes(n_types, k, n))},
+                             xc.options().dtype(torch::kUInt8));
+    check_rc(gphl_segment_mm_tc_f32(xc.data_ptr<float>(), wc.data_ptr<float>(), pc.data_ptr<int32_t>(), n_types, rows, k, n,
+                                    gather.has_value() ? gi.data_ptr<int64_t>() : nullptr, nullptr, 0, ws.data_ptr(),
+                                    y.data_ptr<float>(), stream_of(xc)),
+             "gphl_segment_mm_tc_f32");
+  } else {
+    check_rc(gphl_segment_mm_f32(xc.data_ptr<float>(), wc.data_ptr<float>(), pc.data_ptr<int32_t>(), n_types, rows, k, n,
+                                 gather.has_value() ? gi.data_ptr<int64_t>() : nullptr, y.data_ptr<float>(),
+                                 stream_of(xc)),
+             "gphl_segment_mm_f32");
+  }
   return y;
 }
 

@@ -122,10 +122,13 @@ def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, nor
     destination rows.  ``feature_block`` holds rows ``sl.block_range`` of the node features."""
     lo, hi = sl.block_range
     mine = sl.my_block()
-    if mine.dtype == feature_block.dtype:
-        torch.mm(feature_block, weight, out=mine[:hi - lo])          # project straight into the gather slot
-        mine[:hi - lo].mul_(norm_src_block)
-    else:                                                             # bf16 storage: fp32 product, one rounding
+    if feature_block.is_cuda:
+        from .layers import project
+        if mine.dtype == feature_block.dtype:
+            project(feature_block, weight, norm_src_block, out=mine[:hi - lo])   # straight into the gather slot
+        else:                                                         # bf16 storage: fp32 product, one rounding
+            mine[:hi - lo].copy_(project(feature_block, weight, norm_src_block))
+    else:
         mine[:hi - lo].copy_(torch.mm(feature_block, weight).mul_(norm_src_block))
     full = sl.all_gather()
     if aggregate is None:

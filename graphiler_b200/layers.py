@@ -5,7 +5,8 @@ that model (python/graphiler/mpdfg_optimizer.py:4-16 applied to examples/GAT/GAT
 GCN/GCN.py:21-27, RGCN/RGCN.py:25-33, HGT/HGT.py:28-60), with the further fusions this
 library adds: one fused attention operator for GAT, the node->edge broadcast folded into the
 edge-typed linear and the ``mul`` folded into the segment sum for RGCN / HGT, and a direct
-u_dot_v for HGT.  Dense projections are plain ``torch.mm`` (cuBLAS), as in the reference.
+u_dot_v for HGT.  The GCN projection runs on this library's tensor-core kernel (fp32 accuracy, source scaling in the epilogue); the
+other dense projections are plain ``torch.mm`` (cuBLAS), as in the reference.
 
 ``PreparedGraph`` is the host-side graph handle: device arrays in the reference's DGLGraph
 layout plus cached row-split plans.
@@ -64,9 +65,17 @@ def gcn_norms(pg: PreparedGraph):
     return deg.pow(-0.5).unsqueeze(1)
 
 
+def project(feature, weight, row_scale=None, out=None):
+    """Dense projection ``row_scale * (feature @ weight)``: the tensor-core kernel when the shape allows (the source
+    scaling then rides in its epilogue), cuBLAS otherwise."""
+    if feature.shape[1] % 4 == 0 and feature.is_contiguous() and weight.is_contiguous():
+        return capi.linear(feature, weight, row_scale=None if row_scale is None else row_scale.reshape(-1), out=out)
+    h = torch.mm(feature, weight, out=out) if out is not None else torch.mm(feature, weight)
+    return h if row_scale is None else h.mul_(row_scale.reshape(-1, 1))
+
+
 def gcn_layer(pg: PreparedGraph, feature, weight, norm_src, norm_dst=None, relu: bool = True):
-    h = torch.mm(feature, weight)
-    h.mul_(norm_src)
+    h = project(feature, weight, norm_src)
     scale = None if norm_dst is None else norm_dst.reshape(-1)
     # destination scaling and relu ride in the aggregation kernel's epilogue
     return capi.spmm_gather_sum(pg.g.in_pointer, pg.g.in_node_indices, h, pg.plan_in(h.shape[1]), dst_scale=scale,

@@ -180,6 +180,22 @@ int gphl_segment_mm_f32(const float *x, const float *w, const int32_t *type_poin
                         int64_t m, int64_t k, int64_t n, const int64_t *gather_idx, float *y,
                         void *stream);
 
+/* The same product on the tensor cores (tcgen05.mma, accumulators in tensor memory), with fp32-level
+ * accuracy: operands are split into three bf16 terms and six products are accumulated in fp32.
+ * Optional epilogue: y[i,:] *= row_scale[i] (m floats, may be NULL), then max(., 0) if relu != 0 -
+ * with n_types = 1 and type_pointer = {0, m} this is a dense layer `relu(scale * (x @ w))`.
+ * Needs k % 4 == 0 and 16-byte aligned x, y, workspace (else GPHL_ERR_UNSUPPORTED: use
+ * gphl_segment_mm_f32).  `workspace`: gphl_segment_mm_tc_workspace_bytes(n_types, k, n) bytes of
+ * caller scratch for the split, transposed weights (rewritten by every call). */
+int64_t gphl_segment_mm_tc_workspace_bytes(int64_t n_types, int64_t k, int64_t n);
+int gphl_segment_mm_tc_f32(const float *x, const float *w, const int32_t *type_pointer, int64_t n_types,
+                           int64_t m, int64_t k, int64_t n, const int64_t *gather_idx,
+                           const float *row_scale, int32_t relu, void *workspace, float *y, void *stream);
+/* Barrier waits that ran out inside tensor-core kernels since the library was loaded (0 in a
+ * healthy process; each kernel wait is bounded and a block that gives up frees its tensor memory
+ * and returns).  Synchronises the device. */
+int gphl_tc_wait_timeouts(int *count);
+
 #ifdef __cplusplus
 }
 #endif

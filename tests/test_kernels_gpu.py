@@ -223,18 +223,52 @@ def test_broadcasts_bit_exact(dtype, shape):
     assert torch.equal(capi.gather_rows(g.etype_COO, xe), xe[g.etype_COO])
 
 
-@pytest.mark.parametrize("k,n", [(16, 16), (128, 128), (20, 7), (1, 1), (64, 200)])
-def test_segment_mm(k, n):
-    counts = [0, 130, 1, 0, 700, 63, 64, 65]
+@pytest.mark.parametrize("k,n", [(16, 16), (128, 128), (20, 7), (1, 1), (64, 200), (256, 256), (100, 40)])
+@pytest.mark.parametrize("tensor_cores", [False, True])
+def test_segment_mm(k, n, tensor_cores):
+    if tensor_cores and k % 4:
+        pytest.skip("the tensor-core kernel needs k % 4 == 0")
+    counts = [0, 130, 1, 0, 700, 63, 64, 65, 128, 257]
     m, t = sum(counts), len(counts)
     ptr = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32)
     x = torch.randn(m, k, device=DEV)
     w = torch.randn(t, k, n, device=DEV) / max(1, k) ** 0.5
-    y = capi.segment_mm(x, w, ptr.to(DEV))
-    close(y, O.segment_mm(x, w, ptr))
+    def check(got, truth, xin, scale=None):
+        if not tensor_cores:
+            return close(got, truth)                    # compensated SIMT kernel: the library's default tolerance
+        # The tensor core truncates when it adds into its fp32 accumulator, so an output that cancels to ~0 from
+        # partial sums of order 1 can miss atol 1e-6 by an ulp of the partial sum.  Allowed on top of the default
+        # tolerance: 2 eps of sum_k |x_k||w_k| (any fp32 GEMM, the reference's cuBLAS call included, has sqrt(K) eps).
+        mag = O.segment_mm(np.abs(xin.cpu().numpy()), np.abs(w.cpu().numpy()), ptr)
+        if scale is not None:
+            mag = mag * scale
+        err = np.abs(got.cpu().numpy().astype(np.float64) - truth)
+        assert (err <= ATOL + RTOL * np.abs(truth) + 2 * 2.0 ** -24 * mag).all(), float(err.max())
+
+    y = capi.segment_mm(x, w, ptr.to(DEV), tensor_cores=tensor_cores)
+    check(y, O.segment_mm(x, w, ptr), x)
     gi = torch.randint(0, m, (m,), device=DEV)
-    y2 = capi.segment_mm(x, w, ptr.to(DEV), gather_idx=gi)
-    close(y2, O.segment_mm(x.cpu()[gi.cpu()], w, ptr))
+    y2 = capi.segment_mm(x, w, ptr.to(DEV), gather_idx=gi, tensor_cores=tensor_cores)
+    check(y2, O.segment_mm(x.cpu()[gi.cpu()], w, ptr), x[gi])
+    sc = torch.rand(m, device=DEV) + 0.5
+    y3 = capi.segment_mm(x, w, ptr.to(DEV), row_scale=sc, relu=True, tensor_cores=tensor_cores)
+    scn = sc.cpu().numpy().astype(np.float64)[:, None]
+    check(y3, np.maximum(O.segment_mm(x, w, ptr) * scn, 0), x, scn)
+    assert capi.tc_wait_timeouts() == 0
+
+
+def test_segment_mm_tensor_cores_as_dense_layer_with_large_values():
+    """One type covering all rows = a dense layer; inputs spanning many orders of magnitude keep fp32-level accuracy."""
+    m, k, n = 1000, 256, 256
+    x = torch.randn(m, k, device=DEV) * torch.logspace(-3, 3, m, device=DEV).unsqueeze(1)
+    w = torch.randn(1, k, n, device=DEV) / 16
+    ptr = torch.tensor([0, m], dtype=torch.int32, device=DEV)
+    y = capi.segment_mm(x, w, ptr, tensor_cores=True)
+    truth = x.double().cpu().numpy() @ w[0].double().cpu().numpy()
+    err = np.abs(y.cpu().numpy() - truth)
+    bound = 1e-6 * (np.abs(x.double().cpu().numpy()) @ np.abs(w[0].double().cpu().numpy()))   # ~16 eps of the magnitude sum
+    assert (err <= bound + 1e-30).all()
+    assert capi.tc_wait_timeouts() == 0
 
 
 @pytest.mark.parametrize("name,scale", [("c1", 0.25), ("c2", 0.05), ("c3", 0.05), ("c4", 0.02), ("c5", 0.002)])
