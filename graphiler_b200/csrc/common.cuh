@@ -116,6 +116,64 @@ struct Acc {
   __device__ __forceinline__ float value() const { return __fadd_rn(hi, lo); }
 };
 
+// Packed pairs of fp32 (sm_100 add/sub/mul/fma.f32x2): one instruction issues two IEEE operations, which
+// halves the issue slots of the compensated accumulation.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &a, float &b) {
+  asm("mov.b64 {%0,%1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fsub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fneg2(uint64_t a) { return a ^ 0x8000000080000000ull; }
+
+// Two compensated accumulators side by side (see Acc): the same operations, element-wise on a pair.
+struct Acc2 {
+  uint64_t hi, lo;
+  __device__ __forceinline__ void add(uint64_t v) {
+    const uint64_t s = fadd2(hi, v), bb = fsub2(s, hi);
+    const uint64_t e = fadd2(fsub2(hi, fsub2(s, bb)), fsub2(v, bb));
+    hi = s;
+    lo = fadd2(lo, e);
+  }
+  __device__ __forceinline__ void fma_exact(uint64_t a, uint64_t b) {
+    const uint64_t p = fmul2(a, b);
+    const uint64_t pe = ffma2(a, b, fneg2(p));
+    const uint64_t s = fadd2(hi, p), bb = fsub2(s, hi);
+    const uint64_t e = fadd2(fsub2(hi, fsub2(s, bb)), fsub2(p, bb));
+    hi = s;
+    lo = fadd2(lo, fadd2(e, pe));
+  }
+  __device__ __forceinline__ void merge(uint64_t ohi, uint64_t olo) {
+    const uint64_t s = fadd2(hi, ohi), bb = fsub2(s, hi);
+    const uint64_t e = fadd2(fsub2(hi, fsub2(s, bb)), fsub2(ohi, bb));
+    hi = s;
+    lo = fadd2(lo, fadd2(e, olo));
+  }
+  __device__ __forceinline__ uint64_t value() const { return fadd2(hi, lo); }
+};
+
 __device__ __forceinline__ float leaky(float v, float slope) { return v >= 0.f ? v : v * slope; }
 
 // Online-softmax pair (running maximum, sum of exp(x - maximum)).

@@ -38,38 +38,37 @@ struct GatherArgs {
 
 constexpr int WARPS = 8;
 
-// Raw 16-byte vector of a row; elements are widened to fp32 only when they are accumulated, so
+// Raw 16-byte vector of a row; elements are widened to fp32 pairs only when they are accumulated, so
 // loads in flight cost four registers each whatever the storage type.
 template <typename T>
-__device__ __forceinline__ void unpack(const uint4 &r, float (&v)[VecOf<T>::N]);
+__device__ __forceinline__ void unpack_pairs(const uint4 &r, uint64_t (&v)[VecOf<T>::N / 2]);
 template <>
-__device__ __forceinline__ void unpack<float>(const uint4 &r, float (&v)[4]) {
-  v[0] = __uint_as_float(r.x), v[1] = __uint_as_float(r.y), v[2] = __uint_as_float(r.z), v[3] = __uint_as_float(r.w);
+__device__ __forceinline__ void unpack_pairs<float>(const uint4 &r, uint64_t (&v)[2]) {
+  v[0] = pack2(__uint_as_float(r.x), __uint_as_float(r.y));
+  v[1] = pack2(__uint_as_float(r.z), __uint_as_float(r.w));
 }
 template <>
-__device__ __forceinline__ void unpack<__nv_bfloat16>(const uint4 &r, float (&v)[8]) {
+__device__ __forceinline__ void unpack_pairs<__nv_bfloat16>(const uint4 &r, uint64_t (&v)[4]) {
   const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
+  for (int i = 0; i < 4; ++i) v[i] = pack2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
 }
 
 // EXACT: compensated (two-sum) accumulation, the default contract of the library.  !EXACT: plain
 // fp32 adds (opt-in; the same arithmetic as the reference's kernels, a third of the instructions).
+// Both work on packed pairs of columns.
 template <bool EXACT>
 struct AccT;
 template <>
-struct AccT<true> : Acc {};
+struct AccT<true> : Acc2 {};
 template <>
 struct AccT<false> {
-  float hi;
-  static constexpr float lo = 0.f;
-  __device__ __forceinline__ void add(float v) { hi = __fadd_rn(hi, v); }
-  __device__ __forceinline__ void fma_exact(float a, float b) { hi = __fmaf_rn(a, b, hi); }
-  __device__ __forceinline__ void merge(float ohi, float) { hi = __fadd_rn(hi, ohi); }
-  __device__ __forceinline__ float value() const { return hi; }
+  uint64_t hi;
+  static constexpr uint64_t lo = 0;
+  __device__ __forceinline__ void add(uint64_t v) { hi = fadd2(hi, v); }
+  __device__ __forceinline__ void fma_exact(uint64_t a, uint64_t b) { hi = ffma2(a, b, hi); }
+  __device__ __forceinline__ void merge(uint64_t ohi, uint64_t) { hi = fadd2(hi, ohi); }
+  __device__ __forceinline__ uint64_t value() const { return hi; }
 };
 
 template <typename T, int LPR, int NV, int MODE, bool EXACT>
@@ -100,13 +99,14 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   }
   cols_full = __all_sync(FULL, cols_full);
 
-  AccT<EXACT> acc[NV][VEC];
+  constexpr int VP = VEC / 2;              // packed column pairs per 16-byte vector
+  AccT<EXACT> acc[NV][VP];
 #pragma unroll
   for (int v = 0; v < NV; ++v)
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      acc[v][k].hi = 0.f;
-      if constexpr (EXACT) acc[v][k].lo = 0.f;
+    for (int k = 0; k < VP; ++k) {
+      acc[v][k].hi = 0;
+      if constexpr (EXACT) acc[v][k].lo = 0;
     }
 
   const uint4 *x = static_cast<const uint4 *>(a.x);
@@ -165,15 +165,16 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
       for (int u = 0; u < U; ++u) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          float val[VEC];
-          unpack<T>(raw[u][v], val);
+          uint64_t val[VP];
+          unpack_pairs<T>(raw[u][v], val);
           if (MODE == COPY) {
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) acc[v][k].add(val[k]);
+            for (int k = 0; k < VP; ++k) acc[v][k].add(val[k]);
           } else {
             const float wgt = (e[u] < n) ? wsm[e[u] * a.H + head[v]] : 0.f;
+            const uint64_t w2 = pack2(wgt, wgt);
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) acc[v][k].fma_exact(val[k], wgt);
+            for (int k = 0; k < VP; ++k) acc[v][k].fma_exact(val[k], w2);
           }
         }
       }
@@ -186,9 +187,9 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
 #pragma unroll
     for (int v = 0; v < NV; ++v)
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        const float ohi = __shfl_xor_sync(FULL, acc[v][k].hi, off);
-        const float olo = EXACT ? __shfl_xor_sync(FULL, (float)acc[v][k].lo, off) : 0.f;
+      for (int k = 0; k < VP; ++k) {
+        const uint64_t ohi = __shfl_xor_sync(FULL, (unsigned long long)acc[v][k].hi, off);
+        const uint64_t olo = EXACT ? __shfl_xor_sync(FULL, (unsigned long long)acc[v][k].lo, off) : 0ull;
         // both partners add in the same order (lower group first) and so hold identical values
         if ((lane & off) == 0) {
           acc[v][k].merge(ohi, olo);
@@ -211,8 +212,9 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
       if (!cok[v]) continue;
       float o[VEC];
 #pragma unroll
+      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(), o[2 * k], o[2 * k + 1]);
+#pragma unroll
       for (int k = 0; k < VEC; ++k) {
-        o[k] = acc[v][k].value();
         if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
         if (a.relu) o[k] = fmaxf(o[k], 0.f);
       }
@@ -225,9 +227,12 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
     for (int v = 0; v < NV; ++v) {
       if (!cok[v]) continue;
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        hi[cv[v] * VEC + k] = acc[v][k].hi;
-        lo[cv[v] * VEC + k] = acc[v][k].lo;
+      for (int k = 0; k < VP; ++k) {
+        float h0, h1, l0, l1;
+        unpack2(acc[v][k].hi, h0, h1);
+        unpack2(acc[v][k].lo, l0, l1);
+        hi[cv[v] * VEC + 2 * k] = h0, hi[cv[v] * VEC + 2 * k + 1] = h1;
+        lo[cv[v] * VEC + 2 * k] = l0, lo[cv[v] * VEC + 2 * k + 1] = l1;
       }
     }
   }
