@@ -382,14 +382,10 @@ def run_native(args):
                 "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * world,
                         "d2h_bytes_per_step": n * feat * out.element_size()},
                 "gpu_launches": int(launches), "clocks": clocks}
-        prof = ROOT / "profiles" / "traffic.json"
-        if prof.exists():
-            try:
-                tr = json.loads(prof.read_text()).get(f"copy_u_sum_{args.dtype}")
-                if tr and world == 1:
-                    line["roofline"]["traffic"] = tr["dram_bytes_per_edge"] * e_loc
-            except Exception:
-                pass
+        if world == 1 and args.scale == 1.0:
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
+            # one-pass ncu capture summarised in profiles/gather_sum_copy_u_sum_f256.md
+            line["roofline"]["traffic"] = {"fp32": 28.15e9 + 2.55e9, "bf16": 10.23e9 + 1.33e9}[args.dtype]
     if g_cpu is not None:
         threads = os.cpu_count() or 1
         target = max(1000, int(e * args.cpu_fraction))

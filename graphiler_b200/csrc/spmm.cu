@@ -75,7 +75,7 @@ template <typename T, int LPR, int NV, int MODE, bool EXACT>
 __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   constexpr int VEC = VecOf<T>::N;
   constexpr int G = 32 / LPR;              // neighbour rows streamed concurrently by one warp
-  constexpr int U = (NV >= 4) ? 2 : 4;     // unroll: independent rows in flight per group
+  constexpr int U = (NV >= 4) ? 1 : 4 / NV;  // rows in flight per group: four 16-byte loads per lane (more costs occupancy)
   extern __shared__ float smem_w[];        // WARPS x 32 x H staged edge weights
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
