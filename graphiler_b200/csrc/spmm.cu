@@ -9,6 +9,9 @@
 // before accumulating, which keeps >= U KB per warp in flight.  Sums are compensated
 // (two-sum) fp32 in a fixed order; pieces of a cut row are combined in ascending order by a
 // second small kernel, so the result does not depend on the split or on the GPU count.
+#include <cstdlib>
+#include <string>
+
 #include "common.cuh"
 
 namespace gphl {
@@ -238,6 +241,174 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   }
 }
 
+// ---- bulk-async (TMA) staged variant of the unweighted sum --------------------------------------
+// For rows of >= 512 B.  Each warp owns a ring of BULK_STAGES shared-memory slots, one source row per
+// slot, each guarded by an mbarrier.  An elected lane keeps the ring full with cp.async.bulk copies
+// (the copy engine moves a whole row per instruction and signals the slot's barrier with the byte
+// count), so the rows in flight cost no registers and the accumulation of row j overlaps the
+// fetch of rows j+1 .. j+BULK_STAGES.  No multicast: every copy reads this GPU's memory into this
+// block's shared memory.  Waits are bounded; a wait that runs out sets g_bulk_wait_timeouts, and the
+// warp drains what it issued (bounded again) and leaves its rows unwritten.
+constexpr int BULK_WARPS = 4;
+constexpr uint32_t BULK_WAIT_LIMIT = 1u << 22;
+__device__ int g_bulk_wait_timeouts = 0;
+
+__device__ __forceinline__ uint32_t s_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < BULK_WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+template <typename T, int NV, bool EXACT>
+__global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(GatherArgs a, int stages_log2) {
+  constexpr int VEC = VecOf<T>::N;
+  constexpr int VP = VEC / 2;
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = 1 << stages_log2, smask = stages - 1;   // power of two: slot = j & smask, phase = (j >> log2) & 1
+  const int64_t item_id = (int64_t)blockIdx.x * BULK_WARPS + warp;
+  if (item_id >= a.n_items) return;
+  const Item it = fetch_item(a.items, a.pointer, item_id);
+  const uint32_t row_bytes = (uint32_t)a.FV * 16u;
+  const uint32_t slot_bytes = (row_bytes + 127u) & ~127u;
+  uint8_t *ring = bulk_smem + (size_t)warp * stages * slot_bytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(bulk_smem + (size_t)BULK_WARPS * stages * slot_bytes) + warp * stages;
+  const uint32_t ring_s = s_addr(ring), bars_s = s_addr(bars);
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars_s + 8 * s));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  bool cok[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) cok[v] = v * 32 + lane < a.FV;
+  AccT<EXACT> acc[NV][VP];
+#pragma unroll
+  for (int v = 0; v < NV; ++v)
+#pragma unroll
+    for (int k = 0; k < VP; ++k) {
+      acc[v][k].hi = 0;
+      if constexpr (EXACT) acc[v][k].lo = 0;
+    }
+
+  const uint8_t *x = static_cast<const uint8_t *>(a.x);
+  const int cnt = it.end - it.begin;
+  auto issue = [&](int j, int src) {       // lane 0: fetch source row `src` into the slot of edge j
+    const uint32_t bar = bars_s + 8 * (j & smask), dst = ring_s + (j & smask) * slot_bytes;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(x + (int64_t)src * row_bytes), "r"(row_bytes), "r"(bar)
+                 : "memory");
+  };
+  // indices: lanes hold the batch of 32 that contains edge j and the batch after it
+  int cur_idx = 0, nxt_idx = 0;
+  if (lane < cnt) cur_idx = __ldcs(a.idx + it.begin + lane);
+  if (32 + lane < cnt) nxt_idx = __ldcs(a.idx + it.begin + 32 + lane);
+  // prologue: fill the ring (stages <= 32, so these edges are in the first batch or the second)
+  for (int j = 0; j < min(stages, cnt); ++j) {
+    const int src = __shfl_sync(FULL, j < 32 ? cur_idx : nxt_idx, j & 31);
+    if (lane == 0) issue(j, src);
+  }
+  bool ok = true;
+  for (int j = 0; j < cnt; ++j) {
+    if ((j & 31) == 0 && j > 0) {            // entering the next batch of indices
+      cur_idx = nxt_idx;
+      nxt_idx = (j + 32 + lane < cnt) ? __ldcs(a.idx + it.begin + j + 32 + lane) : 0;
+    }
+    const int stage = j & smask;
+    ok = bar_wait(bars_s + 8 * stage, (uint32_t)((j >> stages_log2) & 1));
+    if (!__all_sync(FULL, ok)) {
+      ok = false;
+      break;
+    }
+    const uint4 *slot = reinterpret_cast<const uint4 *>(ring + (size_t)stage * slot_bytes);
+    uint4 raw[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) raw[v] = cok[v] ? slot[v * 32 + lane] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      uint64_t val[VP];
+      unpack_pairs<T>(raw[v], val);
+#pragma unroll
+      for (int k = 0; k < VP; ++k) acc[v][k].add(val[k]);
+    }
+    // every lane has consumed its part of the slot (the adds above depend on the loads): refill it
+    const int jn = j + stages;
+    const int src = __shfl_sync(FULL, (jn >> 5) == (j >> 5) ? cur_idx : nxt_idx, jn & 31);
+    if (jn < cnt && lane == 0) issue(jn, src);
+  }
+  if (!ok) {
+    if (lane == 0) atomicAdd(&g_bulk_wait_timeouts, 1);
+    for (int s = 0; s < stages; ++s) bar_wait(bars_s + 8 * s, 0), bar_wait(bars_s + 8 * s, 1);   // bounded drain
+    return;
+  }
+
+  if (it.slot < 0) {
+    T *y = static_cast<T *>(a.y) + (int64_t)it.row * a.F;
+    const float scale = a.dst_scale ? __ldg(a.dst_scale + it.row) : 1.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (!cok[v]) continue;
+      float o[VEC];
+#pragma unroll
+      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(), o[2 * k], o[2 * k + 1]);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
+        if (a.relu) o[k] = fmaxf(o[k], 0.f);
+      }
+      VecOf<T>::store(y + (int64_t)(v * 32 + lane) * VEC, o);
+    }
+  } else {
+    float *hi = a.scratch + (int64_t)(2 * it.slot) * a.plane;
+    float *lo = hi + a.plane;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (!cok[v]) continue;
+#pragma unroll
+      for (int k = 0; k < VP; ++k) {
+        float h0, h1, l0, l1;
+        unpack2(acc[v][k].hi, h0, h1);
+        unpack2(acc[v][k].lo, l0, l1);
+        const int c = (v * 32 + lane) * VEC + 2 * k;
+        hi[c] = h0, hi[c + 1] = h1, lo[c] = l0, lo[c + 1] = l1;
+      }
+    }
+  }
+}
+
+template <typename T, int NV, bool EXACT>
+static int launch_bulk_e(const GatherArgs &a, cudaStream_t stream) {
+  const uint32_t slot_bytes = ((uint32_t)a.FV * 16u + 127u) & ~127u;
+  int stages_log2 = 4;                                                  // up to 16 rows in flight per warp,
+  while (stages_log2 > 1 && (size_t)BULK_WARPS * (1 << stages_log2) * slot_bytes > 32 * 1024) --stages_log2;   // <= 32 KB per block
+  const int stages = 1 << stages_log2;
+  const size_t smem = (size_t)BULK_WARPS * stages * slot_bytes + (size_t)BULK_WARPS * stages * 8;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(gather_sum_bulk_kernel<T, NV, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(GPHL_ERR_CUDA, "gather_sum_bulk: shared memory opt-in: %s", cudaGetErrorString(e));
+  }
+  const unsigned grid = (unsigned)((a.n_items + BULK_WARPS - 1) / BULK_WARPS);
+  gather_sum_bulk_kernel<T, NV, EXACT><<<grid, BULK_WARPS * 32, smem, stream>>>(a, stages_log2);
+  return launched("gather_sum_bulk_kernel");
+}
+
+template <typename T, int NV>
+static int launch_bulk(const GatherArgs &a, cudaStream_t stream) {
+  return a.exact ? launch_bulk_e<T, NV, true>(a, stream) : launch_bulk_e<T, NV, false>(a, stream);
+}
+
 // Any shape / alignment: one thread per (item, column), serial over the piece.
 template <typename T, int MODE>
 __global__ void gather_sum_scalar_kernel(GatherArgs a, int32_t D) {
@@ -341,6 +512,15 @@ static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t
   if (vec_ok) {
     a.FV = a.F / VEC;
     a.DV = (MODE == COPY) ? a.FV : D / VEC;
+    static const bool use_bulk = [] {
+      const char *e = getenv("GPHL_GATHER");
+      return e && std::string(e) == "bulk";
+    }();
+    if (MODE == COPY && use_bulk && a.FV >= 32 && a.FV <= 128) {
+      if (a.FV <= 32) rc = launch_bulk<T, 1>(a, stream);
+      else if (a.FV <= 64) rc = launch_bulk<T, 2>(a, stream);
+      else rc = launch_bulk<T, 4>(a, stream);
+    } else
     if (a.FV <= 1) rc = launch_vec<T, MODE, 1, 1>(a, stream);
     else if (a.FV <= 2) rc = launch_vec<T, MODE, 2, 1>(a, stream);
     else if (a.FV <= 4) rc = launch_vec<T, MODE, 4, 1>(a, stream);

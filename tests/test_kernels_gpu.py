@@ -9,8 +9,11 @@ from graphiler_b200 import capi, synthetic
 from graphiler_b200.graph import debug_graph, debug_hetero_graph, prepare_graph
 from oracle import ops_oracle as O
 
+from pathlib import Path
+
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
+ROOT = Path(__file__).resolve().parent.parent
 RTOL, ATOL = 1e-5, 1e-6
 
 
@@ -91,6 +94,36 @@ def test_spmm_fast_accumulation_is_plain_fp32(graph, feat):
     mag = O.spmm_src(x.abs(), graph.in_pointer, graph.in_node_indices)
     err = np.abs(y.cpu().numpy().astype(np.float64) - truth)
     assert (err <= 1e-6 * (1 + mag)).all()
+
+
+def test_spmm_bulk_async_staged_variant_matches_default():
+    """GPHL_GATHER=bulk selects the cp.async.bulk + mbarrier staged kernel for rows >= 512 B (read once per process, so
+    the check runs in a child process): same bits as the default vector-load kernel."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch, sys; sys.path.insert(0, '.');"
+        "from graphiler_b200 import capi, synthetic;"
+        "wl = synthetic.make_c5(scale=0.003); g = wl.graph.to('cuda:0');"
+        "out = {};"
+        "\nfor f, dt in ((256, torch.float32), (128, torch.float32), (256, torch.bfloat16), (512, torch.float32)):"
+        "\n    x = torch.randn(g.num_nodes, f, generator=torch.Generator().manual_seed(f)).to(dt).to('cuda:0')"
+        "\n    plan = capi.Plan(g.in_pointer, f, chunk=64)"
+        "\n    y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan, relu=True)"
+        "\n    out[f'{f}_{dt}'] = y.cpu()"
+        "\ntorch.save(out, sys.argv[1])")
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        paths = {}
+        for mode in ("ldg", "bulk"):
+            paths[mode] = os.path.join(d, mode + ".pt")
+            env = dict(os.environ, GPHL_GATHER=mode)
+            subprocess.run([sys.executable, "-c", code, paths[mode]], check=True, env=env, cwd=str(ROOT), timeout=600)
+        a, b = torch.load(paths["ldg"]), torch.load(paths["bulk"])
+        assert a.keys() == b.keys() and len(a) == 4
+        for k in a:
+            assert torch.equal(a[k], b[k]), k
 
 
 @pytest.mark.parametrize("feat", [16, 128])
