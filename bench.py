@@ -193,6 +193,40 @@ def extras_per_config(dev):
     def t(fn, iters=50, warm=10):
         return time_loop(fn, iters, warm, torch.cuda.synchronize)
 
+    def graphed(fn, iters=50):
+        """The same layer replayed from a CUDA graph (one launch per replay): what the layer costs once the
+        per-kernel launch latency of a small graph is amortised."""
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(s)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            fn()
+        return t(gr.replay, iters, 5)
+
+    # c5 variants: GAT layer (8 heads x 32) and the bf16-storage aggregation kernels
+    w = synthetic.make_c5(device=dev)
+    pg = layers.PreparedGraph(w.graph)
+    p, hy, g = w.params, w.hyper, w.graph
+    n, e, H = g.num_nodes, g.num_edges, int(hy["heads"])
+    ms_gat = t(lambda: layers.gat_layer(pg, w.feats, p["fc_weight"], p["attn_src"], p["attn_dst"], hy["slope"]), iters=10, warm=3)
+    z, el, er = layers.gat_projections(w.feats, p["fc_weight"], p["attn_src"], p["attn_dst"])
+    plan = pg.plan_in(256)
+    st = torch.empty(2 * n * H, device=dev)
+    ms_k = t(lambda: capi.gat_fused(g.in_pointer, g.in_node_indices, pg.in_eid, el, er, z, hy["slope"], plan, stats=st), iters=10, warm=3)
+    b_alg = (n + 1) * 4 + e * 4 + 2 * n * H * 4 + 2 * n * 256 * 4
+    zb = z.bfloat16()
+    ms_kb = t(lambda: capi.gat_fused(g.in_pointer, g.in_node_indices, None, el, er, zb, hy["slope"], plan, stats=st), iters=10, warm=3)
+    ms_sb = t(lambda: capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, zb, plan), iters=10, warm=3)
+    out["c5_gat"] = {"layer_ms": ms_gat, "gat_fused_ms": ms_k, "gat_fused_gbs": b_alg / ms_k / 1e6,
+                     "gat_fused_frac": b_alg / ms_k / 1e6 / hbm, "gat_fused_bf16_ms": ms_kb,
+                     "copy_u_sum_bf16_ms": ms_sb, "copy_u_sum_bf16_gbs": ((n + 1) * 4 + e * 4 + 2 * n * 256 * 2) / ms_sb / 1e6,
+                     "nodes": n, "edges": e}
+    del w, pg, z, el, er, zb, st, plan
+    torch.cuda.empty_cache()
     # c1 GAT
     w = synthetic.make_c1(device="cpu").to(dev)
     pg = layers.PreparedGraph(w.graph)
@@ -207,6 +241,8 @@ def extras_per_config(dev):
     ms_k = t(lambda: capi.gat_fused(g.in_pointer, g.in_node_indices, pg.in_eid, el, er, z, hy["slope"], plan))
     b_alg = (n + 1) * 4 + e * 4 + 2 * n * H * 4 + 2 * n * F * 4
     out["c1_gat"] = {"layer_ms": ms_layer, "layer_ms_unfused_ops": ms_unf, "gat_fused_ms": ms_k,
+                     "layer_ms_cuda_graph": graphed(lambda: layers.gat_layer(pg, w.feats, p["fc_weight"], p["attn_src"],
+                                                                             p["attn_dst"], hy["slope"])),
                      "gat_fused_gbs": b_alg / ms_k / 1e6, "gat_fused_frac": b_alg / ms_k / 1e6 / hbm,
                      "nodes": n, "edges": e}
     # c2 GCN (two layers)

@@ -49,6 +49,7 @@ SIGNATURES = {
     "gphl_gat_fused_ex_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, c_int32, _P, _P, _P,
                                       _P]),
     "gphl_gat_fused_ex_bf16": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, c_int32, _P, _P, _P]),
+    "gphl_gat_head_scores_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P]),
     "gphl_gather_rows_i64": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_gather_rows_i32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_segment_mm_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, _P]),
@@ -271,6 +272,21 @@ def gat_fused(pointer, node_idx, edge_idx, el, er, z, slope: float, plan: Option
                                                 f // heads, _ptr(el), _ptr(er), _ptr(z), float(slope), flags, _ptr(y),
                                                 _ptr(stats), _stream(z)), "gat_fused_bf16")
     return y
+
+
+def gat_head_scores(z, attn_src, attn_dst, el=None, er=None):
+    """el[n,h] = sum_d z[n,h,d] attn_src[h,d], er likewise: the dense prologue of the GAT layer, one pass over z."""
+    _dev(z, attn_src, attn_dst, el, er)
+    heads, dim = attn_src.shape
+    n = z.shape[0]
+    if _feat(z) != heads * dim:
+        raise GphlError("z must have heads * dim columns")
+    el = el if el is not None else torch.empty((n, heads), dtype=torch.float32, device=z.device)
+    er = er if er is not None else torch.empty((n, heads), dtype=torch.float32, device=z.device)
+    with torch.cuda.device(z.device):
+        _check(lib().gphl_gat_head_scores_f32(_ptr(z), _ptr(attn_src), _ptr(attn_dst), n, heads, dim, _ptr(el), _ptr(er),
+                                              _stream(z)), "gat_head_scores")
+    return el, er
 
 
 def gather_rows(idx, x, idx2=None, out=None):

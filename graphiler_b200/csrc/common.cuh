@@ -174,6 +174,8 @@ struct Acc2 {
   __device__ __forceinline__ uint64_t value() const { return fadd2(hi, lo); }
 };
 
+__device__ __forceinline__ bool aligned16_dev(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 __device__ __forceinline__ float leaky(float v, float slope) { return v >= 0.f ? v : v * slope; }
 
 // Online-softmax pair (running maximum, sum of exp(x - maximum)).

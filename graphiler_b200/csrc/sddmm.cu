@@ -119,3 +119,51 @@ extern "C" int gphl_sddmm_u_dot_v_f32_i32(const int32_t *src, const int32_t *dst
                                           int64_t dim, const float *l, const float *r, float *z, void *stream) {
   return u_dot_v<int32_t>(src, dst, n_edges, heads, dim, l, r, z, stream);
 }
+
+// ---- attention scores per node and head: el[n,h] = sum_d z[n,h,d] a_src[h,d], er likewise with a_dst ----
+// The dense prologue of the GAT layer (the reference computes it as mm(z, attn_weight) after its split pass,
+// examples/GAT/GAT.py:25-31).  One sub-warp group of `lanes` threads per node row reads the row once with 16-byte
+// loads and produces both score vectors; products are accumulated exactly (compensated) and reduced with shuffles.
+namespace gphl {
+
+__global__ void head_scores_kernel(const float *__restrict__ z, const float *__restrict__ a_src,
+                                   const float *__restrict__ a_dst, int64_t n, int32_t H, int32_t D,
+                                   float *__restrict__ el, float *__restrict__ er) {
+  // one thread per (node, head): D is small (8..64) and consecutive threads read consecutive heads of a row
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n * H) return;
+  const int h = (int)(t % H);
+  const float *row = z + t * D;                      // (n*H + h) * D
+  const float *as = a_src + (int64_t)h * D, *ad = a_dst + (int64_t)h * D;
+  Acc s{0.f, 0.f}, d{0.f, 0.f};
+  if ((D & 3) == 0 && aligned16_dev(row)) {
+    for (int k = 0; k < D; k += 4) {
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(row + k));
+      s.fma_exact(v.x, __ldg(as + k)), s.fma_exact(v.y, __ldg(as + k + 1));
+      s.fma_exact(v.z, __ldg(as + k + 2)), s.fma_exact(v.w, __ldg(as + k + 3));
+      d.fma_exact(v.x, __ldg(ad + k)), d.fma_exact(v.y, __ldg(ad + k + 1));
+      d.fma_exact(v.z, __ldg(ad + k + 2)), d.fma_exact(v.w, __ldg(ad + k + 3));
+    }
+  } else {
+    for (int k = 0; k < D; ++k) {
+      const float v = __ldg(row + k);
+      s.fma_exact(v, __ldg(as + k));
+      d.fma_exact(v, __ldg(ad + k));
+    }
+  }
+  el[t] = s.value();
+  er[t] = d.value();
+}
+
+}  // namespace gphl
+
+extern "C" int gphl_gat_head_scores_f32(const float *z, const float *attn_src, const float *attn_dst, int64_t n_nodes,
+                                        int64_t heads, int64_t dim, float *el, float *er, void *stream_) {
+  GPHL_REQUIRE(n_nodes >= 0 && heads >= 1 && dim >= 1 && heads * dim < (1 << 20), "bad sizes");
+  if (n_nodes == 0) return GPHL_OK;
+  GPHL_REQUIRE(z && attn_src && attn_dst && el && er, "null pointer argument");
+  const int64_t total = n_nodes * heads;
+  gphl::head_scores_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      z, attn_src, attn_dst, n_nodes, (int32_t)heads, (int32_t)dim, el, er);
+  return gphl::launched("head_scores_kernel");
+}

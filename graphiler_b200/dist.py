@@ -83,6 +83,7 @@ class ShardedLayer:
         dev = in_pointer.device
         # persistent (world*block, feat) buffer; rows >= num_nodes are padding that no index refers to
         self.gathered = torch.zeros((self.world * self.block, feat), dtype=dtype, device=dev)
+        self._extra = {}
         self.plan = None
         if make_plan and in_pointer.is_cuda:
             from . import capi
@@ -102,6 +103,23 @@ class ShardedLayer:
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered, self.my_block(), group=self.group)
         return self.gathered
+
+    def extra_buffer(self, name: str, width: int, dtype=None) -> torch.Tensor:
+        """A further persistent (world*block, width) gather buffer (attention logits of the GAT layer); float32
+        unless it was created with another dtype."""
+        buf = self._extra.get(name)
+        if dtype is None:
+            dtype = buf.dtype if buf is not None else torch.float32
+        if buf is None or buf.shape[1] != width or buf.dtype != dtype:
+            buf = self._extra[name] = torch.zeros((self.world * self.block, width), dtype=dtype, device=self.gathered.device)
+        return buf
+
+    def all_gather_extra(self, name: str) -> torch.Tensor:
+        buf = self._extra[name]
+        if self.world > 1:
+            lo = self.rank * self.block
+            dist.all_gather_into_tensor(buf, buf[lo:lo + self.block], group=self.group)
+        return buf
 
     def gather_outputs(self, local_out: torch.Tensor) -> torch.Tensor:
         """Concatenate every rank's output rows in rank order (testing / export helper)."""
@@ -140,3 +158,34 @@ def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, nor
     if norm_dst_local is not None:
         y.mul_(norm_dst_local.to(y.dtype))
     return torch.relu_(y) if relu else y
+
+
+def gat_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, fc_weight, attn_src, attn_dst, slope: float,
+                      aggregate: Optional[Callable] = None):
+    """One GAT layer on this rank: project the local source block (z, el, er), all-gather the three, then run the
+    fused attention operator over the local destination rows.  er is needed for the local *destination* rows, whose
+    edge-balanced range differs from the equal source block, so it is gathered too (N x H floats)."""
+    lo, hi = sl.block_range
+    heads, dim = attn_src.shape
+    mine = sl.my_block()
+    el_buf, er_buf = sl.extra_buffer("el", heads), sl.extra_buffer("er", heads)
+    b0 = sl.rank * sl.block
+    if feature_block.is_cuda:
+        from . import capi
+        from .layers import project
+        z = project(feature_block, fc_weight, out=mine[:hi - lo])         # straight into the gather slot
+        capi.gat_head_scores(z, attn_src.contiguous(), attn_dst.contiguous(), el=el_buf[b0:b0 + hi - lo],
+                             er=er_buf[b0:b0 + hi - lo])
+    else:
+        z = torch.mm(feature_block, fc_weight)
+        zv = z.view(-1, heads, dim)
+        el_buf[b0:b0 + hi - lo] = (zv * attn_src).sum(-1)
+        er_buf[b0:b0 + hi - lo] = (zv * attn_dst).sum(-1)
+        mine[:hi - lo].copy_(z)
+    full_z = sl.all_gather()
+    full_el, full_er = sl.all_gather_extra("el"), sl.all_gather_extra("er")
+    er_local = full_er[sl.shard.row0:sl.shard.row1]
+    if aggregate is None:
+        from . import capi
+        return capi.gat_fused(sl.shard.pointer, sl.shard.node_indices, None, full_el, er_local, full_z, slope, sl.plan)
+    return aggregate(sl.shard, full_el, er_local, full_z)

@@ -86,10 +86,8 @@ def gat_projections(feature, fc_weight, attn_src, attn_dst):
     """z = h W, el[n,h] = sum_d z[n,h,d] a_src[h,d], er likewise (per-head form of the reference's
     ``mm(cat(z_s, z_d), attn_weight)`` after the optimizer's split pass)."""
     heads, dim = attn_src.shape
-    z = torch.mm(feature, fc_weight)
-    zv = z.view(-1, heads, dim)
-    el = (zv * attn_src).sum(-1)
-    er = (zv * attn_dst).sum(-1)
+    z = project(feature, fc_weight)
+    el, er = capi.gat_head_scores(z, attn_src.contiguous(), attn_dst.contiguous())
     return z, el, er
 
 

@@ -160,6 +160,14 @@ int gphl_gat_fused_ex_bf16(const gphl_plan *plan, const int32_t *pointer, const 
                            const void *z, float slope, int32_t flags, void *out, float *stats,
                            void *stream);
 
+/* Per-node attention scores of the GAT layer: el[n,h] = sum_d z[n,h,d] * attn_src[h,d] and er
+ * likewise with attn_dst (the reference computes them as mm(z, attn_weight) on the two halves of
+ * its attention vector, examples/GAT/GAT.py:25-31 after the optimizer's split pass,
+ * src/optimizer/split.cpp:9-33).  z (n_nodes, heads*dim), attn_* (heads, dim), el / er (n_nodes,
+ * heads).  One pass over z. */
+int gphl_gat_head_scores_f32(const float *z, const float *attn_src, const float *attn_dst, int64_t n_nodes,
+                             int64_t heads, int64_t dim, float *el, float *er, void *stream);
+
 /* ---- broadcasts: y[i,:] = x[idx[i],:] (row gather of row_bytes bytes) -------------------
  * my_ops::BroadcastSrcNode / DstNode / NodeType / EdgeType (broadcast.cu:58-100, ATen
  * advanced indexing there); the composed SrcNodeType / DstNodeType forms pass idx2 so that

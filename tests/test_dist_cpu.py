@@ -50,10 +50,30 @@ def _worker(rank, world, port, tmp):
 
     y = gd.gcn_layer_sharded(sl, x[lo:hi], w, norm[lo:hi], norm[r0:r1], aggregate=aggregate)
     full = sl.gather_outputs(y)
+    # GAT: z, el and er are gathered; the fused operator runs on the local destination rows
+    c1 = synthetic.make_c1(scale=0.02)
+    g1, p1 = c1.graph, {k: v.double() for k, v in c1.params.items()}
+    sl1 = gd.ShardedLayer(g1.in_pointer, g1.in_node_indices, g1.num_nodes, p1["fc_weight"].shape[1], dtype=torch.float64,
+                          rank=rank, world=world, make_plan=False)
+    lo1, hi1 = sl1.block_range
+    sl1.extra_buffer("el", 8, torch.float64), sl1.extra_buffer("er", 8, torch.float64)
+
+    def gat_aggregate(shard, el, er_local, z):
+        eid = torch.arange(shard.nnz)
+        return torch.from_numpy(O.gat_fused(el.numpy(), er_local.numpy(), z.numpy(), 0.2, shard.pointer, shard.node_indices, eid))
+
+    yg = gd.gat_layer_sharded(sl1, c1.feats.double()[lo1:hi1], p1["fc_weight"], p1["attn_src"], p1["attn_dst"], 0.2,
+                              aggregate=gat_aggregate)
+    full_gat = sl1.gather_outputs(yg)
     if rank == 0:
         h = (x @ w) * norm
         want = np.maximum(O.spmm_src(h.numpy(), g.in_pointer, g.in_node_indices) * norm.numpy(), 0)
-        np.save(tmp + "/ok.npy", np.array([np.array_equal(full.numpy(), want), full.shape[0] == g.num_nodes]))
+        z1 = c1.feats.double() @ p1["fc_weight"]
+        zv = z1.view(-1, 8, 8)
+        want_gat = O.gat_fused(((zv * p1["attn_src"]).sum(-1)).numpy(), ((zv * p1["attn_dst"]).sum(-1)).numpy(), z1.numpy(),
+                               0.2, g1.in_pointer, g1.in_node_indices, g1.in_edge_indices)
+        np.save(tmp + "/ok.npy", np.array([np.array_equal(full.numpy(), want), full.shape[0] == g.num_nodes,
+                                            np.allclose(full_gat.numpy(), want_gat, rtol=1e-12, atol=1e-14)]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -63,4 +83,4 @@ def test_sharded_gcn_layer_two_gloo_ranks(world, tmp_path):
     port = 29500 + os.getpid() % 2000
     mp.start_processes(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True, start_method="spawn")
     ok = np.load(tmp_path / "ok.npy")
-    assert ok.all()
+    assert ok.all(), ok

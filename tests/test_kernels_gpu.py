@@ -228,6 +228,16 @@ def test_gat_fused(graph, heads, dim, use_plan):
     close(out2, truth)
 
 
+@pytest.mark.parametrize("heads,dim", [(8, 8), (8, 32), (1, 64), (3, 5)])
+def test_gat_head_scores(heads, dim):
+    z = torch.randn(1000, heads * dim, device=DEV)
+    a_s, a_d = torch.randn(heads, dim, device=DEV), torch.randn(heads, dim, device=DEV)
+    el, er = capi.gat_head_scores(z, a_s, a_d)
+    zv = z.double().cpu().view(-1, heads, dim)
+    close(el, (zv * a_s.double().cpu()).sum(-1).numpy())
+    close(er, (zv * a_d.double().cpu()).sum(-1).numpy())
+
+
 def test_gat_fused_bf16():
     graph = hub_graph()
     g = graph.to(DEV)
