@@ -217,6 +217,15 @@ __global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a) {
     // the tensor core must be done reading the previous slab before it is overwritten; a wait that runs
     // out is recorded and acted on by all threads together after the next block-wide barrier
     if (s > 0 && !mbar_wait(bar, (uint32_t)((s - 1) & 1))) s_failed = 1;
+    // weight slab: 3 copies x ncols rows x 8 chunks, already bf16 and K-major in global memory; asynchronous
+    // 16-byte copies straight into the swizzled layout
+    for (int sp = 0; sp < 3; ++sp) {
+      const __nv_bfloat16 *wsrc = wsplit + sp * wsplit_stride + s * TC_SLAB + c * 8;
+      for (int n = tid >> 3; n < ncols; n += TC_THREADS / 8) {
+        const uint32_t dst = smem_u32(sB + sp * b_split_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(wsrc + (int64_t)n * a.Kpad) : "memory");
+      }
+    }
     // x slab: split and store the three bf16 copies (swizzled: 16-byte chunk c of row r goes to chunk c ^ (r % 8))
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -230,15 +239,6 @@ __global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a) {
       *reinterpret_cast<uint4 *>(sA + off) = o1;
       *reinterpret_cast<uint4 *>(sA + A_SPLIT_BYTES + off) = o2;
       *reinterpret_cast<uint4 *>(sA + 2 * A_SPLIT_BYTES + off) = o3;
-    }
-    // weight slab: 3 copies x ncols rows x 8 chunks, already bf16 and K-major in global memory; asynchronous
-    // 16-byte copies straight into the swizzled layout
-    for (int sp = 0; sp < 3; ++sp) {
-      const __nv_bfloat16 *wsrc = wsplit + sp * wsplit_stride + s * TC_SLAB + c * 8;
-      for (int n = tid >> 3; n < ncols; n += TC_THREADS / 8) {
-        const uint32_t dst = smem_u32(sB + sp * b_split_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(wsrc + (int64_t)n * a.Kpad) : "memory");
-      }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the stores visible to the tensor core
@@ -284,28 +284,42 @@ __global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a) {
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
       for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(__fadd_rn(__uint_as_float(v[q]), __uint_as_float(u[q])));
-      if (r < rows) {
-        float *yrow = a.y + (int64_t)(row0 + r) * a.N + n0 + c0;
-        const bool vec = ((a.N & 3) == 0);
+      // A thread holds 32 columns of its own row; storing them directly would make every store instruction touch
+      // 32 different rows.  The 32 x 32 block goes through a swizzled staging buffer (the x slab's shared memory
+      // is free by now) and leaves as whole 128-byte row segments: 8 lanes per row, 4 rows per instruction.
+      uint8_t *stg = sA + warp * 4096;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float o[4];
+      for (int q = 0; q < 8; ++q) {
+        float o[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            o[e] = __uint_as_float(v[q * 4 + e]);
-            if (a.row_scale) o[e] = __fmul_rn(o[e], scale);
-            if (a.relu) o[e] = fmaxf(o[e], 0.f);
-          }
-          const int col = n0 + c0 + q * 4;
+        for (int e = 0; e < 4; ++e) {
+          o[e] = __uint_as_float(v[q * 4 + e]);
+          if (a.row_scale) o[e] = __fmul_rn(o[e], scale);
+          if (a.relu) o[e] = fmaxf(o[e], 0.f);
+        }
+        *reinterpret_cast<float4 *>(stg + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(o[0], o[1], o[2], o[3]);
+      }
+      __syncwarp();
+      const int ch = lane & 7;
+      const bool vec = ((a.N & 3) == 0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int rr = (lane >> 3) + 4 * j;
+        const float4 o = *reinterpret_cast<const float4 *>(stg + rr * 128 + ((ch ^ (rr & 7)) << 4));
+        const int grow = (warp & 3) * 32 + rr, col = n0 + c0 + ch * 4;
+        if (grow < rows) {
+          float *dst = a.y + (int64_t)(row0 + grow) * a.N + col;
           if (vec && col + 3 < a.N) {
-            *reinterpret_cast<float4 *>(yrow + q * 4) = make_float4(o[0], o[1], o[2], o[3]);
+            __stcs(reinterpret_cast<float4 *>(dst), o);
           } else {
+            const float oo[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              if (col + e < a.N) yrow[q * 4 + e] = o[e];
+              if (col + e < a.N) dst[e] = oo[e];
           }
         }
       }
+      __syncwarp();
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -17,7 +17,7 @@ import torch
 
 from . import capi, layers, synthetic
 
-KERNELS = ("copy_u_sum", "copy_e_sum", "u_mul_e_sum", "u_add_v", "u_dot_v", "segment_softmax", "gat_fused",
+KERNELS = ("linear", "copy_u_sum", "copy_e_sum", "u_mul_e_sum", "u_add_v", "u_dot_v", "segment_softmax", "gat_fused",
            "broadcast_src", "segment_mm_node", "segment_mm_edge")
 
 
@@ -34,7 +34,15 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
     x = torch.randn(n, feat, generator=gen, device=device).to(td)
     d = feat // heads
     flops = None
-    if kernel == "copy_u_sum":
+    if kernel == "linear":                      # dense projection (n, feat) @ (feat, feat) with a row-scale epilogue
+        w = synthetic.glorot((feat, feat), gen, device)
+        sc = torch.rand(n, generator=gen, device=device) + 0.5
+        xf = x.float()
+        y = torch.empty(n, feat, device=device)
+        fn = lambda: capi.linear(xf, w, row_scale=sc, out=y)
+        b_alg = 2 * n * feat * 4 + feat * feat * 4 + n * 4
+        flops = 2 * n * feat * feat
+    elif kernel == "copy_u_sum":
         plan = pg.plan_in(feat)
         fn = lambda: capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan, fast_accum=fast)
         b_alg = (n + 1) * 4 + e * 4 + 2 * n * feat * s
