@@ -56,6 +56,8 @@ SIGNATURES = {
     "gphl_segment_mm_tc_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "gphl_segment_mm_tc_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, c_int32, _P, _P, _P]),
     "gphl_tc_wait_timeouts": (c_int, [POINTER(c_int)]),
+    "gphl_debug_wait_selftest": (c_int, [c_int32, _P]),
+    "gphl_debug_reset_wait_timeouts": (c_int, []),
 }
 
 

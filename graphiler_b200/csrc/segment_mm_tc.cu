@@ -373,6 +373,45 @@ extern "C" int gphl_segment_mm_tc_f32(const float *x, const float *w, const int3
   return launched("segment_mm_tc_kernel");
 }
 
+// Self-test of the bounded wait: one warp waits, with a short poll limit, on an mbarrier that nothing ever
+// completes; the wait must give up, count the timeout and return, leaving the context usable.
+namespace gphl {
+__global__ void wait_selftest_kernel(uint32_t polls) {
+  __shared__ uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  bool done = false;
+  for (uint32_t i = 0; i < polls && !done; ++i) {
+    uint32_t d;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(d)
+        : "r"(b), "r"(0u)
+        : "memory");
+    done = d != 0;
+  }
+  if (!done && threadIdx.x == 0) atomicAdd(&g_tc_wait_timeouts, 1);
+}
+}  // namespace gphl
+
+extern "C" int gphl_debug_wait_selftest(int32_t polls, void *stream) {
+  GPHL_REQUIRE(polls >= 1 && polls <= (1 << 20), "polls must be in [1, 2^20]");
+  gphl::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>((uint32_t)polls);
+  return gphl::launched("wait_selftest_kernel");
+}
+
+extern "C" int gphl_debug_reset_wait_timeouts(void) {
+  const int zero = 0;
+  GPHL_CUDA(cudaMemcpyToSymbol(gphl::g_tc_wait_timeouts, &zero, sizeof(int)));
+  return GPHL_OK;
+}
+
 // Number of barrier waits that ran out in tensor-core kernels since the library was loaded
 // (0 in a healthy process).  Synchronises the device.
 extern "C" int gphl_tc_wait_timeouts(int *count) {

@@ -50,17 +50,20 @@ __global__ void __launch_bounds__(SW * 32) segment_stats_kernel(StatsArgs a) {
     ms.init();
     const float erv = (GAT_LOGITS && hok) ? __ldg(a.er + (int64_t)it.row * a.H + h) : 0.f;
     if (hok) {
-      for (int i = it.begin + eg; i < it.end; i += epw) {
-        float v;
+      auto logit = [&](int i) {
         if (GAT_LOGITS) {
           const int src = __ldg(a.idx + i);
-          v = leaky(__ldg(a.el + (int64_t)src * a.H + h) + erv, a.slope);
-        } else {
-          const int eid = a.eidx ? __ldg(a.eidx + i) : i;
-          v = __ldg(a.x + (int64_t)eid * a.H + h);
+          return leaky(__ldg(a.el + (int64_t)src * a.H + h) + erv, a.slope);
         }
-        ms.push(v);
+        const int eid = a.eidx ? __ldg(a.eidx + i) : i;
+        return __ldg(a.x + (int64_t)eid * a.H + h);
+      };
+      int i = it.begin + eg;
+      for (; i + 3 * epw < it.end; i += 4 * epw) {        // four dependent index -> value chains in flight
+        const float v0 = logit(i), v1 = logit(i + epw), v2 = logit(i + 2 * epw), v3 = logit(i + 3 * epw);
+        ms.push(v0), ms.push(v1), ms.push(v2), ms.push(v3);
       }
+      for (; i < it.end; i += epw) ms.push(logit(i));
     }
     __syncwarp();
     for (int off = a.Hp; off < 32; off <<= 1) {

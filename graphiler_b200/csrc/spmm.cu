@@ -177,7 +177,13 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
             const float wgt = (e[u] < n) ? wsm[e[u] * a.H + head[v]] : 0.f;
             const uint64_t w2 = pack2(wgt, wgt);
 #pragma unroll
-            for (int k = 0; k < VP; ++k) acc[v][k].fma_exact(val[k], w2);
+            for (int k = 0; k < VP; ++k) {
+              // attention weights are softmax probabilities: the rounded products sum to at most max|x| in
+              // magnitude, so their rounding (<= eps/2 of that) is far below tolerance and only the sum is
+              // compensated; arbitrary edge weights (u_mul_e_sum) keep the exact product
+              if (MODE == GAT) acc[v][k].add(fmul2(val[k], w2));
+              else acc[v][k].fma_exact(val[k], w2);
+            }
           }
         }
       }

@@ -203,6 +203,10 @@ int gphl_segment_mm_tc_f32(const float *x, const float *w, const int32_t *type_p
  * healthy process; each kernel wait is bounded and a block that gives up frees its tensor memory
  * and returns).  Synchronises the device. */
 int gphl_tc_wait_timeouts(int *count);
+/* Exercises that give-up path without any fault: launches one warp that waits, for at most `polls`
+ * polls (<= 2^20), on a barrier nothing completes; it must return and raise the counter above by one. */
+int gphl_debug_wait_selftest(int32_t polls, void *stream);
+int gphl_debug_reset_wait_timeouts(void); /* sets the counter back to 0 (synchronises) */
 
 #ifdef __cplusplus
 }

@@ -332,6 +332,19 @@ def test_ops_on_config_shaped_graphs(name, scale):
     close(a, O.segment_softmax(w.cpu() * 5, graph.in_pointer, graph.in_edge_indices))
 
 
+def test_bounded_wait_gives_up_and_reports():
+    """Failure detection without a fault: a wait on a barrier that nothing completes runs out after its poll limit,
+    is counted, and the context stays usable."""
+    before = capi.tc_wait_timeouts()
+    capi._check(capi.lib().gphl_debug_wait_selftest(2000, None), "wait selftest")
+    torch.cuda.synchronize()
+    assert capi.tc_wait_timeouts() == before + 1
+    x = torch.randn(16, 4, device=DEV)
+    assert torch.equal(capi.gather_rows(torch.arange(16, device=DEV), x), x)
+    # restore the "healthy process" reading other tests assert on
+    capi.lib().gphl_debug_reset_wait_timeouts()
+
+
 def test_argument_errors_are_reported_not_fatal():
     g = debug_graph().to(DEV)
     x = torch.randn(3, 8, device=DEV)
