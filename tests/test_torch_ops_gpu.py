@@ -1,0 +1,119 @@
+"""Every operator of the TorchScript registration library (libgraphiler.so), called through torch.ops.my_ops on a
+GPU and checked against the CPU oracle: the reference's fifteen registrations (src/ops/**) plus this library's three
+additions, on the reference's debug_hetero-shaped fixture and a seeded random graph with hub and empty rows."""
+import numpy as np
+import pytest
+import torch
+
+from graphiler_b200 import capi
+from graphiler_b200.graph import attach_types, debug_hetero_graph, prepare_graph
+from oracle import ops_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    torch.classes.load_library(str(capi.TORCH_OPS_LIB))
+    torch.ops.load_library(str(capi.TORCH_OPS_LIB))
+    return torch.ops.my_ops
+
+
+def typed_random_graph():
+    g = torch.Generator().manual_seed(5)
+    n, e = 120, 900
+    src = torch.cat([torch.randint(0, n, (e,), generator=g), torch.randint(0, n, (700,), generator=g)])
+    dst = torch.cat([torch.randint(0, n // 2, (e,), generator=g), torch.full((700,), 11)])
+    gr = prepare_graph(src, dst, n)
+    return attach_types(gr, ntype_counts=[50, 40, 30], etype_counts=[400, 0, 700, 500])
+
+
+def to_obj(g):
+    d = g.to(DEV)
+    obj = torch.classes.my_classes.DGLGraph(d.in_pointer, d.in_node_indices, d.in_edge_indices, d.out_pointer,
+                                            d.out_node_indices, d.out_edge_indices, d.COO_src, d.COO_dst, None, None)
+    obj.SetNtypePointer(d.ntype_pointer), obj.SetEtypePointer(d.etype_pointer)
+    obj.SetNtypeCOO(d.ntype_COO), obj.SetEtypeCOO(d.etype_COO)
+    return obj
+
+
+def close(got, truth, rtol=1e-5, atol=1e-6):
+    ok, bad, err = O.within_tolerance(got.float().cpu().numpy(), truth, rtol, atol)
+    assert ok, f"{bad} elements outside tolerance (max abs err {err:.2e})"
+
+
+@pytest.mark.parametrize("make", [debug_hetero_graph, typed_random_graph])
+def test_all_registered_operators(ops, make):
+    g = make()
+    G = to_obj(g)
+    n, e, tn, te = g.num_nodes, g.num_edges, g.num_ntypes, g.num_etypes
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(n, 16, generator=gen)
+    xd = x.to(DEV)
+    # broadcasts: bit exact, any trailing shape
+    assert torch.equal(ops.BroadcastSrcNode(xd, G).cpu(), x[g.COO_src])
+    assert torch.equal(ops.BroadcastDstNode(xd, G).cpu(), x[g.COO_dst])
+    xt = torch.randn(tn, 4, 4, generator=gen)
+    assert torch.equal(ops.BroadcastNodeType(xt.to(DEV), G).cpu(), xt[g.ntype_COO])
+    assert torch.equal(ops.BroadcastSrcNodeType(xt.to(DEV), G).cpu(), xt[g.ntype_COO][g.COO_src])
+    assert torch.equal(ops.BroadcastDstNodeType(xt.to(DEV), G).cpu(), xt[g.ntype_COO][g.COO_dst])
+    xe = torch.randn(te, 3, generator=gen)
+    assert torch.equal(ops.BroadcastEdgeType(xe.to(DEV), G).cpu(), xe[g.etype_COO])
+    assert ops.get_feat_dim(torch.zeros(5, 3, 4)) == 12
+    # SpMM family
+    close(ops.SpMMSrc(xd, [1], False, None, G), O.spmm_src(x, g.in_pointer, g.in_node_indices))
+    m = torch.randn(e, 16, generator=gen)
+    close(ops.SpMMEdge(m.to(DEV), [1], False, None, G), O.spmm_edge(m, g.in_pointer, g.in_edge_indices))
+    for w in (torch.randn(e, 1, generator=gen), torch.randn(e, 4, generator=gen)):      # one head / four heads
+        close(ops.gspmm_src_mul_e_sum(xd, w.to(DEV), [1], False, None, G),
+              O.src_mul_e_sum(x, w, g.in_pointer, g.in_node_indices, g.in_edge_indices))
+        close(ops.gspmm_dst_mul_e_sum(xd, w.to(DEV), [1], False, None, G),
+              O.dst_mul_e_sum(x, w, g.out_pointer, g.out_node_indices, g.out_edge_indices))
+    # SDDMM
+    l, r = torch.randn(n, 4, generator=gen), torch.randn(n, 4, generator=gen)
+    z = ops.gsddmm_u_add_v_mul_alpha(l.to(DEV), r.to(DEV), 1, G)
+    assert torch.equal(z.cpu(), l[g.COO_src] + r[g.COO_dst])
+    y2 = torch.randn(n, 16, generator=gen)
+    close(ops.gsddmm_u_dot_v(xd, y2.to(DEV), 4, G), O.sddmm_u_dot_v(x, y2, g.COO_src, g.COO_dst, 4))
+    # segment softmax: (E,1), (E,) and multi-head
+    for shape in ((e, 1), (e,), (e, 4)):
+        s = torch.randn(*shape, generator=gen) * 3
+        out = ops.SegmentSoftmax(s.to(DEV), 1, None, G)
+        assert out.shape == s.shape
+        close(out, O.segment_softmax(s, g.in_pointer, g.in_edge_indices))
+    # typed linear (tensor-core path: K % 4 == 0) and the fused source gather
+    wn, we = torch.randn(tn, 16, 8, generator=gen) / 4, torch.randn(te, 16, 8, generator=gen) / 4
+    tol = dict(rtol=1e-5, atol=3e-6)                  # tensor-core accumulation: see tests/test_kernels_gpu.py
+    close(ops.SegmentMMNode(xd, wn.to(DEV), G), O.segment_mm(x, wn, g.ntype_pointer), **tol)
+    close(ops.SegmentMMEdge(m.to(DEV), we.to(DEV), G), O.segment_mm(m, we, g.etype_pointer), **tol)
+    close(ops.SegmentMMEdgeSrc(xd, we.to(DEV), G), O.segment_mm(x[g.COO_src], we, g.etype_pointer), **tol)
+    # fused attention
+    el, er = torch.randn(n, 4, generator=gen), torch.randn(n, 4, generator=gen)
+    close(ops.gat_fused(el.to(DEV), er.to(DEV), xd, 0.2, G),
+          O.gat_fused(el, er, x, 0.2, g.in_pointer, g.in_node_indices, g.in_edge_indices))
+
+
+def test_operators_reject_cpu_tensors_and_bad_shapes(ops):
+    g = debug_hetero_graph()
+    G = to_obj(g)
+    with pytest.raises(RuntimeError):
+        ops.SpMMSrc(torch.zeros(g.num_nodes, 4), [1], False, None, G)
+    with pytest.raises(RuntimeError):
+        ops.SpMMSrc(torch.zeros(g.num_nodes + 1, 4, device=DEV), [1], False, None, G)
+    with pytest.raises(RuntimeError):
+        ops.SegmentSoftmax(torch.zeros(g.num_edges, 2, device=DEV), 0, None, G)
+    with pytest.raises(RuntimeError):
+        ops.SpMMSrc(torch.zeros(g.num_nodes, 4, device=DEV, dtype=torch.float64), [1], False, None, G)
+    y = ops.SpMMSrc(torch.ones(g.num_nodes, 4, device=DEV), [1], False, None, G)     # still healthy
+    assert torch.equal(y.cpu()[:, 0], g.in_degrees().float())
+
+
+def test_prepare_graph_on_device_matches_host():
+    from graphiler_b200 import synthetic
+    wl = synthetic.make_c3(scale=0.01)
+    g = wl.graph
+    gd = prepare_graph(g.COO_src.to(DEV), g.COO_dst.to(DEV), g.num_nodes)
+    for name in ("in_pointer", "in_node_indices", "in_edge_indices", "out_pointer", "out_node_indices",
+                 "out_edge_indices", "COO_src", "COO_dst"):
+        assert torch.equal(getattr(gd, name).cpu(), getattr(g, name)), name
