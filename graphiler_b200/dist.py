@@ -72,14 +72,26 @@ class ShardedLayer:
     """
 
     def __init__(self, in_pointer, in_node_indices, num_nodes: int, feat: int, dtype=torch.float32,
-                 rank: Optional[int] = None, world: Optional[int] = None, group=None, make_plan: bool = True):
+                 rank: Optional[int] = None, world: Optional[int] = None, group=None, make_plan: bool = True,
+                 chunks: int = 1):
         self.group = group
         self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
         self.num_nodes, self.feat = num_nodes, feat
         self.bounds = edge_balanced_row_ranges(in_pointer, self.world)
         self.shard = shard_rows(in_pointer, in_node_indices, self.bounds[self.rank], self.bounds[self.rank + 1])
-        self.block = block_rows(num_nodes, self.world)
+        # With chunks > 1 every rank's source block is cut into `chunks` pieces that are projected and gathered one
+        # after the other, so the all-gather of piece c runs while piece c+1 is being projected.  The gather buffer
+        # is then piece-major - piece c of every rank, rank-major, then piece c+1 ... - so that each collective
+        # fills one contiguous slab, and the shard's source indices are renumbered to that layout once, here.
+        self.chunks = max(1, int(chunks)) if self.world > 1 else 1
+        self.block = (block_rows(num_nodes, self.world) + self.chunks - 1) // self.chunks * self.chunks
+        self.chunk_rows = self.block // self.chunks
+        if self.chunks > 1:
+            s64 = self.shard.node_indices.to(torch.int64)
+            r, o = s64 // self.block, s64 % self.block
+            pos = ((o // self.chunk_rows) * self.world + r) * self.chunk_rows + o % self.chunk_rows
+            self.shard.node_indices = pos.to(torch.int32)
         dev = in_pointer.device
         # persistent (world*block, feat) buffer; rows >= num_nodes are padding that no index refers to
         self.gathered = torch.zeros((self.world * self.block, feat), dtype=dtype, device=dev)
@@ -95,13 +107,34 @@ class ShardedLayer:
         return lo, min(self.num_nodes, lo + self.block)
 
     def my_block(self) -> torch.Tensor:
-        """View of this rank's slot in the gather buffer: write the projected rows here."""
+        """View of this rank's slot in the gather buffer: write the projected rows here (chunks == 1 only)."""
+        assert self.chunks == 1, "with chunks > 1 use project_and_gather"
         lo = self.rank * self.block
         return self.gathered[lo:lo + self.block]
 
     def all_gather(self):
+        assert self.chunks == 1, "with chunks > 1 use project_and_gather"
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered, self.my_block(), group=self.group)
+        return self.gathered
+
+    def project_and_gather(self, fill: Callable) -> torch.Tensor:
+        """Produce this rank's source rows and assemble everyone's.  ``fill(row_lo, row_hi, out)`` writes rows
+        [row_lo, row_hi) of this rank's block (block-relative) into ``out``.  Piece by piece: the collective of a
+        piece is issued asynchronously right after its rows were produced and overlaps the next piece's ``fill``."""
+        lo, hi = self.block_range
+        n_mine = hi - lo
+        works = []
+        for c in range(self.chunks):
+            slab = self.gathered[c * self.world * self.chunk_rows:(c + 1) * self.world * self.chunk_rows]
+            mine = slab[self.rank * self.chunk_rows:(self.rank + 1) * self.chunk_rows]
+            r0, r1 = c * self.chunk_rows, min((c + 1) * self.chunk_rows, n_mine)
+            if r1 > r0:
+                fill(r0, r1, mine[:r1 - r0])
+            if self.world > 1:
+                works.append(dist.all_gather_into_tensor(slab, mine, group=self.group, async_op=True))
+        for w in works:
+            w.wait()
         return self.gathered
 
     def extra_buffer(self, name: str, width: int, dtype=None) -> torch.Tensor:
@@ -138,17 +171,17 @@ def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, nor
                       relu: bool = True, aggregate: Optional[Callable] = None):
     """One GCN layer on this rank: project the local source block, all-gather, aggregate the local
     destination rows.  ``feature_block`` holds rows ``sl.block_range`` of the node features."""
-    lo, hi = sl.block_range
-    mine = sl.my_block()
-    if feature_block.is_cuda:
-        from .layers import project
-        if mine.dtype == feature_block.dtype:
-            project(feature_block, weight, norm_src_block, out=mine[:hi - lo])   # straight into the gather slot
-        else:                                                         # bf16 storage: fp32 product, one rounding
-            mine[:hi - lo].copy_(project(feature_block, weight, norm_src_block))
-    else:
-        mine[:hi - lo].copy_(torch.mm(feature_block, weight).mul_(norm_src_block))
-    full = sl.all_gather()
+    def fill(r0, r1, out):
+        if feature_block.is_cuda:
+            from .layers import project
+            if out.dtype == feature_block.dtype:
+                project(feature_block[r0:r1], weight, norm_src_block[r0:r1], out=out)   # straight into the gather slot
+            else:                                                       # bf16 storage: fp32 product, one rounding
+                out.copy_(project(feature_block[r0:r1], weight, norm_src_block[r0:r1]))
+        else:
+            out.copy_(torch.mm(feature_block[r0:r1], weight).mul_(norm_src_block[r0:r1]))
+
+    full = sl.project_and_gather(fill)
     if aggregate is None:
         from . import capi
         # destination scaling and relu ride in the aggregation kernel's epilogue
@@ -165,6 +198,7 @@ def gat_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, fc_weight, 
     """One GAT layer on this rank: project the local source block (z, el, er), all-gather the three, then run the
     fused attention operator over the local destination rows.  er is needed for the local *destination* rows, whose
     edge-balanced range differs from the equal source block, so it is gathered too (N x H floats)."""
+    assert sl.chunks == 1, "the GAT layer gathers three tensors in one step: build its ShardedLayer with chunks=1"
     lo, hi = sl.block_range
     heads, dim = attn_src.shape
     mine = sl.my_block()

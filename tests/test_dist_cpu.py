@@ -40,16 +40,19 @@ def _worker(rank, world, port, tmp):
     wl = synthetic.make_c2(scale=0.01)
     g, x, w = wl.graph, wl.feats.double(), wl.params["w1"].double()
     norm = g.in_degrees().clamp(min=1).double().pow(-0.5).unsqueeze(1)
-    sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], dtype=torch.float64,
-                         rank=rank, world=world, make_plan=False)
-    lo, hi = sl.block_range
-    r0, r1 = sl.shard.row0, sl.shard.row1
-
     def aggregate(shard, full):
         return torch.from_numpy(O.spmm_src(full.numpy(), shard.pointer, shard.node_indices))
 
-    y = gd.gcn_layer_sharded(sl, x[lo:hi], w, norm[lo:hi], norm[r0:r1], aggregate=aggregate)
-    full = sl.gather_outputs(y)
+    fulls = []
+    for chunks in (1, 3):                      # one collective per layer, or three overlapped pieces
+        sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], dtype=torch.float64,
+                             rank=rank, world=world, make_plan=False, chunks=chunks)
+        lo, hi = sl.block_range
+        r0, r1 = sl.shard.row0, sl.shard.row1
+        y = gd.gcn_layer_sharded(sl, x[lo:hi], w, norm[lo:hi], norm[r0:r1], aggregate=aggregate)
+        fulls.append(sl.gather_outputs(y))
+    full = fulls[0]
+    assert torch.equal(fulls[0], fulls[1])
     # GAT: z, el and er are gathered; the fused operator runs on the local destination rows
     c1 = synthetic.make_c1(scale=0.02)
     g1, p1 = c1.graph, {k: v.double() for k, v in c1.params.items()}

@@ -29,6 +29,12 @@ def _worker(rank, world, port, tmp):
     full = sl.gather_outputs(y)
     pg = layers.PreparedGraph(g)
     single = layers.gcn_layer(pg, x, w, norm, norm)
+    # the same layer with the projection / all-gather cut into four overlapped pieces
+    s4 = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, chunks=4)
+    lo4, hi4 = s4.block_range
+    y4 = gd.gcn_layer_sharded(s4, x[lo4:hi4].contiguous(), w, norm[lo4:hi4].contiguous(),
+                              norm[s4.shard.row0:s4.shard.row1].contiguous())
+    full4 = s4.gather_outputs(y4)
     # GAT on the same graph: z, el, er gathered, fused attention on the local rows
     p = wl.params
     sg = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, p["fc_weight"].shape[1], rank=rank, world=world)
@@ -41,7 +47,7 @@ def _worker(rank, world, port, tmp):
         # the dense projections run on different row blocks but every row's dot products are computed identically,
         # and the sparse kernels do not depend on the sharding: bit-exact
         np.save(tmp + "/ok.npy", np.array([bool(torch.equal(full, single)), full.shape[0] == g.num_nodes,
-                                            bool(torch.equal(full_gat, single_gat))]))
+                                            bool(torch.equal(full_gat, single_gat)), bool(torch.equal(full4, single))]))
     dist.barrier()
     dist.destroy_process_group()
 
