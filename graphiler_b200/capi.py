@@ -231,7 +231,7 @@ def sddmm_u_dot_v(src, dst, l, r, heads: int, out=None):
 def segment_softmax(pointer, edge_idx, x, plan: Optional[Plan] = None, out=None, stats=None):
     _dev(pointer, edge_idx, x, out, stats)
     n_rows, heads = pointer.numel() - 1, _feat(x)
-    y = out if out is not None else torch.zeros_like(x)
+    y = out if out is not None else torch.empty_like(x)     # every edge id of a valid graph lies in one segment
     if stats is None:
         stats = torch.empty(max(1, 2 * n_rows * heads), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):

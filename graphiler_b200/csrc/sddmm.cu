@@ -4,6 +4,8 @@
 // (u_dot_v); consecutive threads own consecutive outputs of the same edge, so the gathered
 // reads of one endpoint row and the output writes are contiguous.  Dot products are
 // accumulated with an exact-product compensated sum.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace gphl {
@@ -59,6 +61,68 @@ __global__ void u_dot_v_kernel(const I *__restrict__ src, const I *__restrict__ 
   }
 }
 
+// u_dot_v with coalesced row reads: a sub-warp group of LPR lanes reads one edge's two endpoint rows as
+// consecutive 16-byte vectors (the same lane layout as the row-gather SpMM), multiplies exactly, and the DV = D / 4
+// lanes that share a head reduce with shuffles.  32 / LPR edges are in flight per warp instruction, U per group.
+template <typename I, int LPR, int NV>
+__global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__ src, const I *__restrict__ dst,
+                                                           int64_t n_edges, int32_t H, int32_t FV, int32_t DV,
+                                                           const float4 *__restrict__ l, const float4 *__restrict__ r,
+                                                           float *__restrict__ z) {
+  constexpr int G = 32 / LPR, U = (NV >= 2) ? 2 : 4;
+  const int lane = threadIdx.x & 31, g = lane / LPR, ll = lane % LPR;
+  const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t base = warp_id * 32; base < n_edges; base += n_warps * 32) {
+    const int n = (n_edges - base) < 32 ? (int)(n_edges - base) : 32;
+    int64_t my_s = 0, my_d = 0;
+    if (lane < n) my_s = (int64_t)__ldg(src + base + lane), my_d = (int64_t)__ldg(dst + base + lane);
+#pragma unroll 1
+    for (int jj = 0; jj < n; jj += G * U) {
+      float4 a[U][NV], b[U][NV];
+      int e[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        e[u] = jj + u * G + g;
+        const int64_t s_row = __shfl_sync(FULL, my_s, e[u] & 31), d_row = __shfl_sync(FULL, my_d, e[u] & 31);
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const int cv = v * LPR + ll;
+          const bool ok = e[u] < n && cv < FV;
+          a[u][v] = ok ? __ldg(l + s_row * FV + cv) : make_float4(0.f, 0.f, 0.f, 0.f);
+          b[u][v] = ok ? __ldg(r + d_row * FV + cv) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          Acc acc{0.f, 0.f};
+          acc.fma_exact(a[u][v].x, b[u][v].x), acc.fma_exact(a[u][v].y, b[u][v].y);
+          acc.fma_exact(a[u][v].z, b[u][v].z), acc.fma_exact(a[u][v].w, b[u][v].w);
+          for (int off = 1; off < DV; off <<= 1) {            // DV is a power of two <= LPR
+            const float ohi = __shfl_xor_sync(FULL, acc.hi, off), olo = __shfl_xor_sync(FULL, acc.lo, off);
+            acc.merge(ohi, olo);
+          }
+          const int cv = v * LPR + ll;
+          if (e[u] < n && cv < FV && (cv % DV) == 0) z[(base + e[u]) * H + cv / DV] = acc.value();
+        }
+      }
+    }
+  }
+}
+
+template <typename I, int LPR, int NV>
+static int launch_u_dot_v_rows(const I *src, const I *dst, int64_t n_edges, int64_t heads, int64_t fv, int64_t dv,
+                               const float *l, const float *r, float *z, cudaStream_t stream) {
+  const int64_t warps = (n_edges + 31) / 32;
+  const int64_t blocks = std::min<int64_t>((warps + 7) / 8, 148LL * 32);
+  u_dot_v_rows_kernel<I, LPR, NV><<<(unsigned)blocks, 256, 0, stream>>>(
+      src, dst, n_edges, (int32_t)heads, (int32_t)fv, (int32_t)dv, reinterpret_cast<const float4 *>(l),
+      reinterpret_cast<const float4 *>(r), z);
+  return launched("u_dot_v_rows_kernel");
+}
+
 static unsigned grid_for(int64_t total, int block) {
   int64_t g = (total + block - 1) / block;
   const int64_t cap = 148LL * 64;  // grid-stride beyond a few waves of the 148 SMs
@@ -91,6 +155,27 @@ static int u_dot_v(const I *src, const I *dst, int64_t n_edges, int64_t heads, i
   GPHL_REQUIRE(src && dst && l && r && z, "null pointer argument");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int64_t total = n_edges * heads;
+  const int64_t dv = dim / 4, fv = heads * dim / 4;
+  if (dim % 4 == 0 && (dv & (dv - 1)) == 0 && dv <= 32 && fv <= 128 && (dim >= 32 || fv >= 64) && aligned16(l) &&
+      aligned16(r)) {
+    // coalesced path for wide rows / wide heads (measured: at 512-byte rows with 64-byte heads the thread-per-head
+    // kernel below is faster, its reads are still sector-sized): whole rows as 16-byte vectors, heads reduced
+    // across lanes
+    const int64_t lpr = fv <= 1 ? 1 : fv <= 2 ? 2 : fv <= 4 ? 4 : fv <= 8 ? 8 : fv <= 16 ? 16 : 32;
+    if (dv <= lpr) {
+      switch (lpr) {
+        case 1: return launch_u_dot_v_rows<I, 1, 1>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
+        case 2: return launch_u_dot_v_rows<I, 2, 1>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
+        case 4: return launch_u_dot_v_rows<I, 4, 1>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
+        case 8: return launch_u_dot_v_rows<I, 8, 1>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
+        case 16: return launch_u_dot_v_rows<I, 16, 1>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
+        default:
+          if (fv <= 32) return launch_u_dot_v_rows<I, 32, 1>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
+          if (fv <= 64) return launch_u_dot_v_rows<I, 32, 2>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
+          return launch_u_dot_v_rows<I, 32, 4>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
+      }
+    }
+  }
   if (dim % 4 == 0 && aligned16(l) && aligned16(r)) {
     u_dot_v_kernel<I, true><<<grid_for(total, 256), 256, 0, stream>>>(src, dst, n_edges, (int32_t)heads, (int32_t)dim, l, r, z);
   } else {

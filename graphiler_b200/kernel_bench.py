@@ -54,7 +54,7 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
     elif kernel == "u_mul_e_sum":
         w = torch.rand(e, heads, generator=gen, device=device)
         plan = pg.plan_in(feat)
-        fn = lambda: capi.spmm_u_mul_e_sum(g.in_pointer, g.in_node_indices, g.in_edge_indices, x, w, plan)
+        fn = lambda: capi.spmm_u_mul_e_sum(g.in_pointer, g.in_node_indices, pg.in_eid, x, w, plan)
         b_alg = (n + 1) * 4 + 2 * e * 4 + e * heads * 4 + 2 * n * feat * 4
     elif kernel == "u_add_v":
         l = torch.randn(n, heads, generator=gen, device=device)
@@ -70,7 +70,7 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
         plan = pg.plan_in(feat)
         y = torch.empty_like(lg)
         st = torch.empty(2 * n * heads, device=device)
-        fn = lambda: capi.segment_softmax(g.in_pointer, g.in_edge_indices, lg, plan, out=y, stats=st)
+        fn = lambda: capi.segment_softmax(g.in_pointer, pg.in_eid, lg, plan, out=y, stats=st)
         b_alg = (n + 1) * 4 + e * 4 + 2 * e * heads * 4
     elif kernel == "gat_fused":
         el = torch.randn(n, heads, generator=gen, device=device)

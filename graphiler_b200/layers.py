@@ -99,8 +99,8 @@ def gat_layer(pg: PreparedGraph, feature, fc_weight, attn_src, attn_dst, slope: 
         return capi.gat_fused(g.in_pointer, g.in_node_indices, pg.in_eid, el, er, z, slope, plan)
     e = capi.sddmm_u_add_v(g.COO_src, g.COO_dst, el, er)
     e = torch.nn.functional.leaky_relu_(e, slope)
-    a = capi.segment_softmax(g.in_pointer, g.in_edge_indices, e, plan)
-    return capi.spmm_u_mul_e_sum(g.in_pointer, g.in_node_indices, g.in_edge_indices, z, a, plan)
+    a = capi.segment_softmax(g.in_pointer, pg.in_eid, e, plan)         # None: edge ids equal CSC positions
+    return capi.spmm_u_mul_e_sum(g.in_pointer, g.in_node_indices, pg.in_eid, z, a, plan)
 
 
 def rgcn_layer(pg: PreparedGraph, h, weight, norm):
@@ -108,7 +108,7 @@ def rgcn_layer(pg: PreparedGraph, h, weight, norm):
     m = capi.segment_mm(h, weight, g.etype_pointer, gather_idx=g.COO_src)        # (E, out): BroadcastSrcNode fused
     plan = pg.plan_in(m.shape[1])
     # mul(m, norm) folded into the segment sum: rows of m are addressed by edge id
-    return capi.spmm_u_mul_e_sum(g.in_pointer, g.in_edge_indices, g.in_edge_indices, m, norm, plan)
+    return capi.spmm_u_mul_e_sum(g.in_pointer, g.in_edge_indices, pg.in_eid, m, norm, plan)
 
 
 def hgt_layer(pg: PreparedGraph, h, p: Dict[str, torch.Tensor], heads: int, sqrt_dk: float):
@@ -122,8 +122,8 @@ def hgt_layer(pg: PreparedGraph, h, p: Dict[str, torch.Tensor], heads: int, sqrt
     pri = capi.gather_rows(g.etype_COO, p["relation_pri"])
     s = s.mul_(pri).div_(sqrt_dk)
     plan = pg.plan_in(v2.shape[1])
-    a = capi.segment_softmax(g.in_pointer, g.in_edge_indices, s, plan)
-    t = capi.spmm_u_mul_e_sum(g.in_pointer, g.in_edge_indices, g.in_edge_indices, v2, a, plan)
+    a = capi.segment_softmax(g.in_pointer, pg.in_eid, s, plan)
+    t = capi.spmm_u_mul_e_sum(g.in_pointer, g.in_edge_indices, pg.in_eid, v2, a, plan)
     out = capi.segment_mm(t, p["a_weight"], g.ntype_pointer)
     alpha = capi.gather_rows(g.ntype_COO, torch.sigmoid(p["skip"]).unsqueeze(1).contiguous())
     return out.mul_(alpha)
