@@ -73,7 +73,7 @@ class ShardedLayer:
 
     def __init__(self, in_pointer, in_node_indices, num_nodes: int, feat: int, dtype=torch.float32,
                  rank: Optional[int] = None, world: Optional[int] = None, group=None, make_plan: bool = True,
-                 chunks: int = 1):
+                 chunks: int = 1, exchange: str = "allgather"):
         self.group = group
         self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
@@ -84,6 +84,11 @@ class ShardedLayer:
         # after the other, so the all-gather of piece c runs while piece c+1 is being projected.  The gather buffer
         # is then piece-major - piece c of every rank, rank-major, then piece c+1 ... - so that each collective
         # fills one contiguous slab, and the shard's source indices are renumbered to that layout once, here.
+        if exchange not in ("allgather", "halo"):
+            raise ValueError("exchange must be 'allgather' or 'halo'")
+        self.exchange = exchange if self.world > 1 else "allgather"
+        if self.exchange == "halo":
+            chunks = 1
         self.chunks = max(1, int(chunks)) if self.world > 1 else 1
         self.block = (block_rows(num_nodes, self.world) + self.chunks - 1) // self.chunks * self.chunks
         self.chunk_rows = self.block // self.chunks
@@ -93,6 +98,14 @@ class ShardedLayer:
             pos = ((o // self.chunk_rows) * self.world + r) * self.chunk_rows + o % self.chunk_rows
             self.shard.node_indices = pos.to(torch.int32)
         dev = in_pointer.device
+        if self.exchange == "halo":
+            self._setup_halo(feat, dtype, dev)
+            self._extra = {}
+            self.plan = None
+            if make_plan and in_pointer.is_cuda:
+                from . import capi
+                self.plan = capi.Plan(self.shard.pointer, feat)
+            return
         # persistent (world*block, feat) buffer; rows >= num_nodes are padding that no index refers to
         self.gathered = torch.zeros((self.world * self.block, feat), dtype=dtype, device=dev)
         self._extra = {}
@@ -100,6 +113,30 @@ class ShardedLayer:
         if make_plan and in_pointer.is_cuda:
             from . import capi
             self.plan = capi.Plan(self.shard.pointer, feat)
+
+    def _setup_halo(self, feat: int, dtype, dev):
+        """Sparse exchange instead of the all-gather: a shard only reads the source rows that occur in its index
+        array (on a power-law graph cut 8 ways that is well under half of all rows), so every rank tells each owner
+        once which of the owner's rows it needs, and each step the owners pack exactly those rows and one
+        all-to-all delivers them into a compact buffer.  The shard's indices are renumbered to that buffer; the
+        values and their order are unchanged, so results stay bit-identical to the single-GPU layer."""
+        needed = torch.unique(self.shard.node_indices.to(torch.int64))             # sorted: grouped by owner block
+        owner = needed // self.block
+        need_counts = torch.bincount(owner, minlength=self.world)
+        self.recv_counts = need_counts.tolist()
+        send_counts = torch.empty_like(need_counts)
+        dist.all_to_all_single(send_counts, need_counts, group=self.group)
+        self.send_counts = send_counts.tolist()
+        ask = (needed - owner * self.block).contiguous()                          # block-relative row of each request
+        asked = torch.empty(int(sum(self.send_counts)), dtype=torch.int64, device=dev)
+        dist.all_to_all_single(asked, ask, output_split_sizes=self.send_counts, input_split_sizes=self.recv_counts,
+                               group=self.group)
+        self.send_rows = asked                                                    # rows of my block, grouped by requester
+        self.shard.node_indices = torch.searchsorted(needed, self.shard.node_indices.to(torch.int64)).to(torch.int32)
+        self.proj = torch.zeros((self.block, feat), dtype=dtype, device=dev)       # my projected block
+        self.send_buf = torch.empty((asked.numel(), feat), dtype=dtype, device=dev)
+        self.gathered = torch.empty((needed.numel(), feat), dtype=dtype, device=dev)   # compact: only the rows this shard reads
+        self.halo_rows = int(needed.numel())
 
     @property
     def block_range(self):
@@ -124,6 +161,16 @@ class ShardedLayer:
         piece is issued asynchronously right after its rows were produced and overlaps the next piece's ``fill``."""
         lo, hi = self.block_range
         n_mine = hi - lo
+        if self.exchange == "halo":
+            fill(0, n_mine, self.proj[:n_mine])
+            if self.proj.is_cuda:
+                from . import capi
+                capi.gather_rows(self.send_rows, self.proj, out=self.send_buf)    # pack the requested rows
+            else:
+                torch.index_select(self.proj, 0, self.send_rows, out=self.send_buf)
+            dist.all_to_all_single(self.gathered, self.send_buf, output_split_sizes=self.recv_counts,
+                                   input_split_sizes=self.send_counts, group=self.group)
+            return self.gathered
         works = []
         for c in range(self.chunks):
             slab = self.gathered[c * self.world * self.chunk_rows:(c + 1) * self.world * self.chunk_rows]
@@ -198,7 +245,8 @@ def gat_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, fc_weight, 
     """One GAT layer on this rank: project the local source block (z, el, er), all-gather the three, then run the
     fused attention operator over the local destination rows.  er is needed for the local *destination* rows, whose
     edge-balanced range differs from the equal source block, so it is gathered too (N x H floats)."""
-    assert sl.chunks == 1, "the GAT layer gathers three tensors in one step: build its ShardedLayer with chunks=1"
+    assert sl.chunks == 1 and sl.exchange == "allgather", \
+        "the GAT layer gathers three tensors in one step: build its ShardedLayer with chunks=1, exchange='allgather'"
     lo, hi = sl.block_range
     heads, dim = attn_src.shape
     mine = sl.my_block()

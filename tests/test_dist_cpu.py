@@ -44,15 +44,16 @@ def _worker(rank, world, port, tmp):
         return torch.from_numpy(O.spmm_src(full.numpy(), shard.pointer, shard.node_indices))
 
     fulls = []
-    for chunks in (1, 3):                      # one collective per layer, or three overlapped pieces
+    # one collective per layer, three overlapped pieces, or the sparse (halo) exchange of only the rows a shard reads
+    for chunks, exchange in ((1, "allgather"), (3, "allgather"), (1, "halo")):
         sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], dtype=torch.float64,
-                             rank=rank, world=world, make_plan=False, chunks=chunks)
+                             rank=rank, world=world, make_plan=False, chunks=chunks, exchange=exchange)
         lo, hi = sl.block_range
         r0, r1 = sl.shard.row0, sl.shard.row1
         y = gd.gcn_layer_sharded(sl, x[lo:hi], w, norm[lo:hi], norm[r0:r1], aggregate=aggregate)
         fulls.append(sl.gather_outputs(y))
     full = fulls[0]
-    assert torch.equal(fulls[0], fulls[1])
+    assert torch.equal(fulls[0], fulls[1]) and torch.equal(fulls[0], fulls[2])
     # GAT: z, el and er are gathered; the fused operator runs on the local destination rows
     c1 = synthetic.make_c1(scale=0.02)
     g1, p1 = c1.graph, {k: v.double() for k, v in c1.params.items()}

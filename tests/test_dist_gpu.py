@@ -35,6 +35,12 @@ def _worker(rank, world, port, tmp):
     y4 = gd.gcn_layer_sharded(s4, x[lo4:hi4].contiguous(), w, norm[lo4:hi4].contiguous(),
                               norm[s4.shard.row0:s4.shard.row1].contiguous())
     full4 = s4.gather_outputs(y4)
+    # and with the sparse (halo) exchange: only the source rows a shard reads travel, through one all-to-all
+    sh = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, exchange="halo")
+    loh, hih = sh.block_range
+    yh = gd.gcn_layer_sharded(sh, x[loh:hih].contiguous(), w, norm[loh:hih].contiguous(),
+                              norm[sh.shard.row0:sh.shard.row1].contiguous())
+    fullh = sh.gather_outputs(yh)
     # GAT on the same graph: z, el, er gathered, fused attention on the local rows
     p = wl.params
     sg = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, p["fc_weight"].shape[1], rank=rank, world=world)
@@ -47,7 +53,8 @@ def _worker(rank, world, port, tmp):
         # the dense projections run on different row blocks but every row's dot products are computed identically,
         # and the sparse kernels do not depend on the sharding: bit-exact
         np.save(tmp + "/ok.npy", np.array([bool(torch.equal(full, single)), full.shape[0] == g.num_nodes,
-                                            bool(torch.equal(full_gat, single_gat)), bool(torch.equal(full4, single))]))
+                                            bool(torch.equal(full_gat, single_gat)), bool(torch.equal(full4, single)),
+                                            bool(torch.equal(fullh, single))]))
     dist.barrier()
     dist.destroy_process_group()
 
