@@ -61,12 +61,17 @@ struct Item {
 
 }  // namespace gphl
 
+// Items of at most this many positions are "short": kernels whose per-position work is a few bytes give a short
+// item to a group of threads instead of a whole warp.
+#define GPHL_SHORT_ITEM 64
+
 struct gphl_plan {
   int64_t n_rows = 0;
   int32_t chunk = 0;
   int64_t n_items = 0;
   int64_t n_split_rows = 0;
   int64_t n_pieces = 0;
+  int64_t n_long_items = 0;         // items longer than GPHL_SHORT_ITEM positions (they come first in `items`)
   int64_t max_feat = 0;
   gphl::Item *items = nullptr;      // device, n_items
   int32_t *split_rows = nullptr;    // device, n_split_rows: row id of each cut row

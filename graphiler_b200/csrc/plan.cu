@@ -46,6 +46,7 @@ extern "C" int gphl_plan_create(const int32_t *pointer, int64_t n_rows, int32_t 
   std::vector<int32_t> split_rows, split_ptr;
   split_ptr.push_back(0);
   int32_t slot = 0;
+  int64_t n_long = 0;
   for (int64_t v = 0; v < n_rows; ++v) {
     const int32_t b = ptr[v], e = ptr[v + 1];
     if (e < b) return fail(GPHL_ERR_INVALID_ARGUMENT, "plan_create: pointer array decreases at row %lld", (long long)v);
@@ -65,6 +66,8 @@ extern "C" int gphl_plan_create(const int32_t *pointer, int64_t n_rows, int32_t 
     std::vector<int64_t> start((size_t)chunk + 2, 0);
     for (const Item &it : items) start[(size_t)(chunk - (it.end - it.begin)) + 1]++;
     for (size_t i = 1; i < start.size(); ++i) start[i] += start[i - 1];
+    // buckets are ordered by falling length: the long items are those in front of the first short bucket
+    n_long = chunk > GPHL_SHORT_ITEM ? start[(size_t)(chunk - GPHL_SHORT_ITEM)] : 0;
     std::vector<Item> sorted(items.size());
     for (const Item &it : items) sorted[(size_t)start[(size_t)(chunk - (it.end - it.begin))]++] = it;
     items.swap(sorted);
@@ -76,6 +79,7 @@ extern "C" int gphl_plan_create(const int32_t *pointer, int64_t n_rows, int32_t 
   p->n_items = (int64_t)items.size();
   p->n_split_rows = (int64_t)split_rows.size();
   p->n_pieces = slot;
+  p->n_long_items = n_long;
   // rows are padded to a multiple of 8 columns so that 16-byte accesses to scratch stay aligned
   p->max_feat = (max_feat + 7) / 8 * 8;
   p->scratch_bytes = (int64_t)sizeof(float) * 2 * p->n_pieces * p->max_feat;

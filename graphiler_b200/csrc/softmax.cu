@@ -1,12 +1,14 @@
 // Per-destination (segment) softmax for sm_100a, multi-head, and the statistics half of the
 // fused attention operator.
 //
-// Pass 1 (stats): one warp per work item; lanes are laid out as (edge sub-batch x head) so
-// that the H logits of one edge are one coalesced access; every lane keeps an online
-// (maximum, exp-sum) pair, initialised at -inf, and the sub-batches are merged with
-// shuffles.  Pieces of cut rows leave partial pairs in the plan's scratch and a merge
-// kernel combines them in ascending order.  Pass 2 (normalise) writes exp(x - max) / sum at
-// every edge id.  The fused operator replaces pass 2 by the weighted gather in spmm.cu.
+// Pass 1 (stats): one warp per work item; lanes are laid out as (edge sub-batch x head group) so
+// that the H logits of one edge are one coalesced access (16-byte loads of four heads when H is
+// a multiple of four); every lane keeps online (maximum, exp-sum) pairs, initialised at -inf,
+// and the sub-batches are merged with shuffles.  An item that is a whole row then writes
+// exp(x - max) / sum in a second sweep over the logits it has just read.  Pieces of cut rows
+// leave partial pairs in the plan's scratch, a merge kernel combines them in ascending order and
+// pass 2 (normalise) writes their outputs.  The fused attention operator uses pass 1 only and
+// replaces the rest by the weighted gather in spmm.cu.
 #include <mutex>
 
 #include "common.cuh"
@@ -36,56 +38,189 @@ struct StatsArgs {
 
 constexpr int SW = 8;  // warps per block
 
-template <bool GAT_LOGITS>
+// V consecutive heads of one edge per lane: V = 4 turns the H logits of an edge into 16-byte accesses
+// (heads % 4 == 0 and 16-byte aligned arrays), V = 1 is the general layout.
+template <int V>
+struct HeadVec {
+  float v[V];
+};
+template <int V>
+__device__ __forceinline__ HeadVec<V> load_heads(const float *p) {
+  HeadVec<V> r;
+  if constexpr (V == 4) {
+    const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+    r.v[0] = t.x, r.v[1] = t.y, r.v[2] = t.z, r.v[3] = t.w;
+  } else {
+    r.v[0] = __ldg(p);
+  }
+  return r;
+}
+template <int V>
+__device__ __forceinline__ void store_heads(float *p, const HeadVec<V> &r) {
+  if constexpr (V == 4) *reinterpret_cast<float4 *>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  else *p = r.v[0];
+}
+
+// Pass 1.  NORMALIZE (logits mode only): an item that is a whole row also writes its outputs in
+// a second sweep over the row, which the warp has just pulled through L2, so that pass 2 is
+// left with the pieces of cut rows.
+template <bool GAT_LOGITS, int V, bool NORMALIZE>
 __global__ void __launch_bounds__(SW * 32) segment_stats_kernel(StatsArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t item_id = (int64_t)blockIdx.x * SW + warp;
   if (item_id >= a.n_items) return;
   const Item it = fetch_item(a.items, a.pointer, item_id);
   const int hl = lane % a.Hp, eg = lane / a.Hp, epw = 32 / a.Hp;
-  for (int h0 = 0; h0 < a.H; h0 += a.Hp) {
-    const int h = h0 + hl;
+  for (int h0 = 0; h0 < a.H; h0 += a.Hp * V) {
+    const int h = h0 + hl * V;
     const bool hok = h < a.H;
-    MaxSum ms;
-    ms.init();
-    const float erv = (GAT_LOGITS && hok) ? __ldg(a.er + (int64_t)it.row * a.H + h) : 0.f;
+    MaxSum ms[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) ms[v].init();
+    HeadVec<V> erv;
+#pragma unroll
+    for (int v = 0; v < V; ++v) erv.v[v] = 0.f;
+    if (GAT_LOGITS && hok) erv = load_heads<V>(a.er + (int64_t)it.row * a.H + h);
+    auto logit = [&](int i) {
+      if (GAT_LOGITS) {
+        const int src = __ldg(a.idx + i);
+        HeadVec<V> r = load_heads<V>(a.el + (int64_t)src * a.H + h);
+#pragma unroll
+        for (int v = 0; v < V; ++v) r.v[v] = leaky(r.v[v] + erv.v[v], a.slope);
+        return r;
+      }
+      const int eid = a.eidx ? __ldg(a.eidx + i) : i;
+      return load_heads<V>(a.x + (int64_t)eid * a.H + h);
+    };
     if (hok) {
-      auto logit = [&](int i) {
-        if (GAT_LOGITS) {
-          const int src = __ldg(a.idx + i);
-          return leaky(__ldg(a.el + (int64_t)src * a.H + h) + erv, a.slope);
-        }
-        const int eid = a.eidx ? __ldg(a.eidx + i) : i;
-        return __ldg(a.x + (int64_t)eid * a.H + h);
-      };
       int i = it.begin + eg;
       for (; i + 3 * epw < it.end; i += 4 * epw) {        // four dependent index -> value chains in flight
-        const float v0 = logit(i), v1 = logit(i + epw), v2 = logit(i + 2 * epw), v3 = logit(i + 3 * epw);
-        ms.push(v0), ms.push(v1), ms.push(v2), ms.push(v3);
+        const HeadVec<V> v0 = logit(i), v1 = logit(i + epw), v2 = logit(i + 2 * epw), v3 = logit(i + 3 * epw);
+#pragma unroll
+        for (int v = 0; v < V; ++v) ms[v].push(v0.v[v]), ms[v].push(v1.v[v]), ms[v].push(v2.v[v]), ms[v].push(v3.v[v]);
       }
-      for (; i < it.end; i += epw) ms.push(logit(i));
+      for (; i < it.end; i += epw) {
+        const HeadVec<V> v0 = logit(i);
+#pragma unroll
+        for (int v = 0; v < V; ++v) ms[v].push(v0.v[v]);
+      }
     }
     __syncwarp();
-    for (int off = a.Hp; off < 32; off <<= 1) {
-      const float om = __shfl_xor_sync(FULL, ms.m, off);
-      const float os = __shfl_xor_sync(FULL, ms.s, off);
-      // identical on both partners: merge the lower sub-batch first
-      if ((lane & off) == 0) {
-        ms.merge(om, os);
-      } else {
-        MaxSum t{om, os};
-        t.merge(ms.m, ms.s);
-        ms = t;
-      }
+    // combine the sub-batches: common maximum, rescale each lane's sum to it, add (the butterfly leaves the same
+    // pair on every lane of a head group)
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      float mr = ms[v].m;
+      for (int off = a.Hp; off < 32; off <<= 1) mr = fmaxf(mr, __shfl_xor_sync(FULL, mr, off));
+      float sc = ms[v].s > 0.f ? ms[v].s * expf(ms[v].m - mr) : 0.f;
+      for (int off = a.Hp; off < 32; off <<= 1) sc += __shfl_xor_sync(FULL, sc, off);
+      ms[v].m = mr, ms[v].s = sc;
     }
-    if (eg == 0 && hok) {
-      if (it.slot < 0) {
-        float2 o = ms.s > 0.f ? make_float2(ms.m, 1.f / ms.s) : make_float2(0.f, 0.f);
-        reinterpret_cast<float2 *>(a.stats)[(int64_t)it.row * a.H + h] = o;
-      } else {
-        reinterpret_cast<float2 *>(a.scratch)[(int64_t)it.slot * a.H + h] = make_float2(ms.m, ms.s);
+    if (!hok) continue;
+    if (it.slot >= 0) {
+      if (eg == 0) {
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+          reinterpret_cast<float2 *>(a.scratch)[(int64_t)it.slot * a.H + h + v] = make_float2(ms[v].m, ms[v].s);
       }
+      continue;
     }
+    HeadVec<V> mx, inv;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      const bool any = ms[v].s > 0.f;
+      mx.v[v] = any ? ms[v].m : 0.f, inv.v[v] = any ? 1.f / ms[v].s : 0.f;
+    }
+    if (eg == 0) {
+#pragma unroll
+      for (int v = 0; v < V; ++v)
+        reinterpret_cast<float2 *>(a.stats)[(int64_t)it.row * a.H + h + v] = make_float2(mx.v[v], inv.v[v]);
+    }
+    if (NORMALIZE) {                                       // every lane of a head group holds the row's pair
+      auto emit = [&](int i, const HeadVec<V> &x) {
+        const int eid = a.eidx ? __ldg(a.eidx + i) : i;
+        HeadVec<V> y;
+#pragma unroll
+        for (int v = 0; v < V; ++v) y.v[v] = expf(x.v[v] - mx.v[v]) * inv.v[v];
+        store_heads<V>(a.y + (int64_t)eid * a.H + h, y);
+      };
+      int i = it.begin + eg;
+      for (; i + 3 * epw < it.end; i += 4 * epw) {
+        const HeadVec<V> v0 = logit(i), v1 = logit(i + epw), v2 = logit(i + 2 * epw), v3 = logit(i + 3 * epw);
+        emit(i, v0), emit(i + epw, v1), emit(i + 2 * epw, v2), emit(i + 3 * epw, v3);
+      }
+      for (; i < it.end; i += epw) emit(i, logit(i));
+    }
+  }
+}
+
+// Pass 1 for short items (at most GPHL_SHORT_ITEM positions), which are most rows of a sparse graph: one thread
+// per (item, group of V heads) walks the item's positions, so a warp serves 32 / (H / V) items and the per-item
+// bookkeeping is shared by as many.  The plan orders items by length, so the threads of a warp run equally long.
+// Same arithmetic per (row, head) as the warp kernel up to the order in which positions are combined.
+template <bool GAT_LOGITS, int V, bool NORMALIZE>
+__global__ void __launch_bounds__(256) segment_stats_rows_kernel(StatsArgs a, int64_t first_item, int32_t units) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t item_id = first_item + t / units;
+  if (item_id >= a.n_items) return;
+  const int h = (int)(t % units) * V;
+  const Item it = fetch_item(a.items, a.pointer, item_id);
+  MaxSum ms[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) ms[v].init();
+  HeadVec<V> erv;
+#pragma unroll
+  for (int v = 0; v < V; ++v) erv.v[v] = 0.f;
+  if (GAT_LOGITS) erv = load_heads<V>(a.er + (int64_t)it.row * a.H + h);
+  auto logit = [&](int i) {
+    if (GAT_LOGITS) {
+      const int src = __ldg(a.idx + i);
+      HeadVec<V> r = load_heads<V>(a.el + (int64_t)src * a.H + h);
+#pragma unroll
+      for (int v = 0; v < V; ++v) r.v[v] = leaky(r.v[v] + erv.v[v], a.slope);
+      return r;
+    }
+    const int eid = a.eidx ? __ldg(a.eidx + i) : i;
+    return load_heads<V>(a.x + (int64_t)eid * a.H + h);
+  };
+  int i = it.begin;
+  for (; i + 3 < it.end; i += 4) {
+    const HeadVec<V> v0 = logit(i), v1 = logit(i + 1), v2 = logit(i + 2), v3 = logit(i + 3);
+#pragma unroll
+    for (int v = 0; v < V; ++v) ms[v].push(v0.v[v]), ms[v].push(v1.v[v]), ms[v].push(v2.v[v]), ms[v].push(v3.v[v]);
+  }
+  for (; i < it.end; ++i) {
+    const HeadVec<V> v0 = logit(i);
+#pragma unroll
+    for (int v = 0; v < V; ++v) ms[v].push(v0.v[v]);
+  }
+  if (it.slot >= 0) {
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+      reinterpret_cast<float2 *>(a.scratch)[(int64_t)it.slot * a.H + h + v] = make_float2(ms[v].m, ms[v].s);
+    return;
+  }
+  HeadVec<V> mx, inv;
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const bool any = ms[v].s > 0.f;
+    mx.v[v] = any ? ms[v].m : 0.f, inv.v[v] = any ? 1.f / ms[v].s : 0.f;
+    reinterpret_cast<float2 *>(a.stats)[(int64_t)it.row * a.H + h + v] = make_float2(mx.v[v], inv.v[v]);
+  }
+  if (NORMALIZE) {
+    auto emit = [&](int j, const HeadVec<V> &x) {
+      const int eid = a.eidx ? __ldg(a.eidx + j) : j;
+      HeadVec<V> y;
+#pragma unroll
+      for (int v = 0; v < V; ++v) y.v[v] = expf(x.v[v] - mx.v[v]) * inv.v[v];
+      store_heads<V>(a.y + (int64_t)eid * a.H + h, y);
+    };
+    i = it.begin;
+    for (; i + 3 < it.end; i += 4) {
+      const HeadVec<V> v0 = logit(i), v1 = logit(i + 1), v2 = logit(i + 2), v3 = logit(i + 3);
+      emit(i, v0), emit(i + 1, v1), emit(i + 2, v2), emit(i + 3, v3);
+    }
+    for (; i < it.end; ++i) emit(i, logit(i));
   }
 }
 
@@ -105,31 +240,35 @@ __global__ void stats_merge_kernel(const int32_t *split_rows, const int32_t *spl
   reinterpret_cast<float2 *>(stats)[(int64_t)split_rows[r] * H + h] = o;
 }
 
-__global__ void __launch_bounds__(SW * 32) softmax_normalize_kernel(StatsArgs a) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t item_id = (int64_t)blockIdx.x * SW + warp;
-  if (item_id >= a.n_items) return;
-  const Item it = fetch_item(a.items, a.pointer, item_id);
-  const int hl = lane % a.Hp, eg = lane / a.Hp, epw = 32 / a.Hp;
-  for (int h0 = 0; h0 < a.H; h0 += a.Hp) {
-    const int h = h0 + hl;
-    if (h >= a.H) continue;
-    const float2 st = __ldg(reinterpret_cast<const float2 *>(a.stats) + (int64_t)it.row * a.H + h);
-    for (int i = it.begin + eg; i < it.end; i += epw) {
-      const int eid = a.eidx ? __ldg(a.eidx + i) : i;
-      const int64_t o = (int64_t)eid * a.H + h;
-      a.y[o] = expf(__ldg(a.x + o) - st.x) * st.y;
+// Pass 2 for the cut rows (the others were finished by pass 1): one block per cut row.
+template <int V>
+__global__ void __launch_bounds__(256) softmax_normalize_kernel(StatsArgs a, const int32_t *split_rows) {
+  const int row = __ldg(split_rows + blockIdx.x);
+  const int begin = __ldg(a.pointer + row), end = __ldg(a.pointer + row + 1);
+  const int units = a.H / V;
+  const int64_t total = (int64_t)(end - begin) * units;
+  for (int64_t t = threadIdx.x; t < total; t += blockDim.x) {
+    const int i = begin + (int)(t / units), h = (int)(t % units) * V;
+    const int eid = a.eidx ? __ldg(a.eidx + i) : i;
+    const HeadVec<V> x = load_heads<V>(a.x + (int64_t)eid * a.H + h);
+    HeadVec<V> y;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      const float2 st = __ldg(reinterpret_cast<const float2 *>(a.stats) + (int64_t)row * a.H + h + v);
+      y.v[v] = expf(x.v[v] - st.x) * st.y;
     }
+    store_heads<V>(a.y + (int64_t)eid * a.H + h, y);
   }
 }
 
-static int lanes_per_edge(int64_t H) {
+static int lanes_per_edge(int64_t units) {
   int hp = 1;
-  while (hp < H && hp < 32) hp <<= 1;
+  while (hp < units && hp < 32) hp <<= 1;
   return hp;
 }
 
-template <bool GAT_LOGITS>
+// Statistics of every row; with NORMALIZE also the outputs of the rows that were not cut.
+template <bool GAT_LOGITS, bool NORMALIZE>
 static int run_stats(const gphl_plan *plan, StatsArgs a, int64_t n_rows, cudaStream_t stream) {
   if (plan) {
     a.items = plan->items, a.n_items = plan->n_items, a.scratch = plan->scratch;
@@ -139,15 +278,38 @@ static int run_stats(const gphl_plan *plan, StatsArgs a, int64_t n_rows, cudaStr
   } else {
     a.n_items = n_rows;
   }
-  a.Hp = lanes_per_edge(a.H);
-  segment_stats_kernel<GAT_LOGITS><<<(unsigned)((a.n_items + SW - 1) / SW), SW * 32, 0, stream>>>(a);
-  int rc = launched("segment_stats_kernel");
-  if (rc != GPHL_OK) return rc;
+  const bool vec = a.H % 4 == 0 && (GAT_LOGITS ? aligned16(a.el) && aligned16(a.er) : aligned16(a.x) && aligned16(a.y));
+  a.Hp = lanes_per_edge(vec ? a.H / 4 : a.H);
+  // long items: a warp each; short items (the plan puts them last): a thread per (item, head group)
+  const int64_t n_warp_items = plan ? plan->n_long_items : a.n_items;
+  int rc = GPHL_OK;
+  if (n_warp_items > 0) {
+    StatsArgs w = a;
+    w.n_items = n_warp_items;
+    const unsigned grid = (unsigned)((n_warp_items + SW - 1) / SW);
+    if (vec) segment_stats_kernel<GAT_LOGITS, 4, NORMALIZE><<<grid, SW * 32, 0, stream>>>(w);
+    else segment_stats_kernel<GAT_LOGITS, 1, NORMALIZE><<<grid, SW * 32, 0, stream>>>(w);
+    rc = launched("segment_stats_kernel");
+    if (rc != GPHL_OK) return rc;
+  }
+  if (a.n_items > n_warp_items) {
+    const int32_t units = vec ? a.H / 4 : a.H;
+    const int64_t threads = (a.n_items - n_warp_items) * units;
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    if (vec) segment_stats_rows_kernel<GAT_LOGITS, 4, NORMALIZE><<<grid, 256, 0, stream>>>(a, n_warp_items, units);
+    else segment_stats_rows_kernel<GAT_LOGITS, 1, NORMALIZE><<<grid, 256, 0, stream>>>(a, n_warp_items, units);
+    rc = launched("segment_stats_rows_kernel");
+    if (rc != GPHL_OK) return rc;
+  }
   if (plan && plan->n_split_rows > 0) {
     const int64_t total = plan->n_split_rows * a.H;
     stats_merge_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(plan->split_rows, plan->split_ptr,
                                                                           plan->n_split_rows, a.H, plan->scratch, a.stats);
     rc = launched("stats_merge_kernel");
+    if (rc != GPHL_OK || !NORMALIZE) return rc;
+    if (vec) softmax_normalize_kernel<4><<<(unsigned)plan->n_split_rows, 256, 0, stream>>>(a, plan->split_rows);
+    else softmax_normalize_kernel<1><<<(unsigned)plan->n_split_rows, 256, 0, stream>>>(a, plan->split_rows);
+    rc = launched("softmax_normalize_kernel");
   }
   return rc;
 }
@@ -167,13 +329,7 @@ extern "C" int gphl_segment_softmax_f32(const gphl_plan *plan, const int32_t *po
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   StatsArgs a{};
   a.pointer = pointer, a.eidx = edge_idx, a.x = x, a.y = y, a.stats = stats, a.H = (int32_t)heads;
-  int rc = run_stats<false>(plan, a, n_rows, stream);
-  if (rc != GPHL_OK) return rc;
-  if (plan) a.items = plan->items, a.n_items = plan->n_items;
-  else a.n_items = n_rows;
-  a.Hp = lanes_per_edge(heads);
-  softmax_normalize_kernel<<<(unsigned)((a.n_items + SW - 1) / SW), SW * 32, 0, stream>>>(a);
-  return launched("softmax_normalize_kernel");
+  return run_stats<false, true>(plan, a, n_rows, stream);
 }
 
 static int gat_check(const gphl_plan *plan, const int32_t *pointer, const int32_t *node_idx, int64_t n_rows,
@@ -197,7 +353,7 @@ extern "C" int gphl_gat_fused_ex_f32(const gphl_plan *plan, const int32_t *point
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   StatsArgs a{};
   a.pointer = pointer, a.idx = node_idx, a.el = el, a.er = er, a.slope = slope, a.stats = stats, a.H = (int32_t)heads;
-  rc = run_stats<true>(plan, a, n_rows, stream);
+  rc = run_stats<true, false>(plan, a, n_rows, stream);
   if (rc != GPHL_OK) return rc;
   return gat_aggregate_f32(plan, pointer, node_idx, edge_idx, n_rows, heads, dim, el, er, z, slope, out, alpha_out,
                            stats, flags, stream);
@@ -221,7 +377,7 @@ extern "C" int gphl_gat_fused_ex_bf16(const gphl_plan *plan, const int32_t *poin
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   StatsArgs a{};
   a.pointer = pointer, a.idx = node_idx, a.el = el, a.er = er, a.slope = slope, a.stats = stats, a.H = (int32_t)heads;
-  rc = run_stats<true>(plan, a, n_rows, stream);
+  rc = run_stats<true, false>(plan, a, n_rows, stream);
   if (rc != GPHL_OK) return rc;
   return gat_aggregate_bf16(plan, pointer, node_idx, n_rows, heads, dim, el, er, z, slope, out, stats, flags, stream);
 }

@@ -114,7 +114,19 @@ struct DGLGraph : torch::CustomClassHolder {
     return p;
   }
 
+  // int32 edge positions 0..E-1 and an int32 copy of COO_dst, made on first use (edge-level left operand of e_dot_v)
+  const Tensor &edge_positions32() {
+    if (!edge_pos32.defined())
+      edge_pos32 = torch::arange(num_edges, COO_dst.options().dtype(torch::kInt32));
+    return edge_pos32;
+  }
+  const Tensor &coo_dst32() {
+    if (!dst32.defined()) dst32 = COO_dst.to(torch::kInt32).contiguous();
+    return dst32;
+  }
+
   int64_t num_nodes, num_edges, num_ntypes, num_etypes;
+  Tensor edge_pos32, dst32;
   Tensor in_pointer, in_node_indices, in_edge_indices;
   Tensor out_pointer, out_node_indices, out_edge_indices;
   Tensor COO_src, COO_dst;
@@ -225,6 +237,33 @@ Tensor dst_mul_e_sum(Tensor x, Tensor w, std::vector<int64_t>, bool, c10::option
   return mul_e_sum(x, w, g, false);
 }
 
+// Not registered by the reference.  Replaces SpMMEdge(mul(a, b)): the product of an (E, F) message with an (E, H)
+// per-edge weight (H divides F; either operand order) is folded into the segment sum, so the (E, F) product is never
+// written.  Other shapes multiply first and sum afterwards, as the unfused graph did.
+Tensor SpMMEdgeMul(Tensor a, Tensor b, const GraphPtr &g) {
+  auto edge2d = [&](const Tensor &t) {
+    return t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.dim() == 2 && t.size(0) == g->num_edges;
+  };
+  const Tensor *x = nullptr, *w = nullptr;
+  if (edge2d(a) && edge2d(b)) {
+    if (b.size(1) >= 1 && a.size(1) % b.size(1) == 0 && b.size(1) < a.size(1)) x = &a, w = &b;
+    else if (a.size(1) >= 1 && b.size(1) % a.size(1) == 0 && a.size(1) < b.size(1)) x = &b, w = &a;
+  }
+  if (x == nullptr) return spmm_gather(at::mul(a, b), g->in_edge_indices, g, g->num_edges, "SpMMEdgeMul input");
+  Tensor xc = x->contiguous(), wc = w->contiguous();
+  const int64_t f = xc.size(1), h = wc.size(1);
+  Tensor y = torch::empty({g->num_nodes, f}, xc.options());
+  Tensor ptr = cuda_idx(g->in_pointer, torch::kInt32, "in_pointer");
+  Tensor eid = cuda_idx(g->in_edge_indices, torch::kInt32, "in_edge_indices");
+  c10::cuda::CUDAGuard guard(xc.device());
+  // rows of x and of w are both addressed by edge id
+  check_rc(gphl_spmm_u_mul_e_sum_f32(g->plan(true, f), ptr.data_ptr<int32_t>(), ptr_or<int32_t>(eid, ptr),
+                                     ptr_or<int32_t>(eid, ptr), g->num_nodes, h, f / h, ptr_or<float>(xc, ptr),
+                                     ptr_or<float>(wc, ptr), y.data_ptr<float>(), stream_of(xc)),
+           "gphl_spmm_u_mul_e_sum_f32");
+  return y;
+}
+
 // ---- SDDMM --------------------------------------------------------------------------------
 Tensor u_add_v_mul_alpha(Tensor l, Tensor r, int64_t /*alpha: ignored, as in the reference*/, const GraphPtr &g) {
   Tensor lc = cuda_f32(l, "source features"), rc_ = cuda_f32(r, "destination features");
@@ -252,6 +291,29 @@ Tensor u_dot_v(Tensor l, Tensor r, int64_t heads, const GraphPtr &g) {
   check_rc(gphl_sddmm_u_dot_v_f32_i64(s.data_ptr<int64_t>(), d.data_ptr<int64_t>(), g->num_edges, heads, f / heads,
                                       lc.data_ptr<float>(), rc_.data_ptr<float>(), z.data_ptr<float>(), stream_of(lc)),
            "gphl_sddmm_u_dot_v_f32_i64");
+  return z;
+}
+
+// Not registered by the reference.  Replaces sum(mul(e, BroadcastDstNode(v)), [1], keepdim) where e already holds one
+// row per edge (HGT: the relation-transformed keys): out[i, h] = sum_d e[i, h, d] * v[COO_dst[i], h, d].  Shapes the
+// kernel does not cover take the unfused route so that the rewrite never changes what a graph accepts.
+Tensor e_dot_v(Tensor e, Tensor v, int64_t heads, const GraphPtr &g) {
+  const bool fits = e.is_cuda() && v.is_cuda() && e.scalar_type() == torch::kFloat32 && v.scalar_type() == torch::kFloat32 &&
+                    e.dim() == 2 && v.dim() == 2 && e.size(0) == g->num_edges && v.size(0) == g->num_nodes &&
+                    e.size(1) == v.size(1) && heads >= 1 && e.size(1) % heads == 0 && g->num_edges < INT32_MAX;
+  if (!fits) {
+    TORCH_CHECK(heads == 1, "gsddmm_e_dot_v: the general form needs heads == 1");
+    return at::sum(at::mul(e, gather_rows(v, g->COO_dst, c10::nullopt)), {1}, true);
+  }
+  Tensor ec = e.contiguous(), vc = v.contiguous();
+  const int64_t f = ec.size(1);
+  Tensor z = torch::empty({g->num_edges, heads}, ec.options());
+  if (g->num_edges == 0) return z;
+  c10::cuda::CUDAGuard guard(ec.device());
+  const Tensor &pos = g->edge_positions32(), &dst = g->coo_dst32();
+  check_rc(gphl_sddmm_u_dot_v_f32_i32(pos.data_ptr<int32_t>(), dst.data_ptr<int32_t>(), g->num_edges, heads, f / heads,
+                                      ec.data_ptr<float>(), vc.data_ptr<float>(), z.data_ptr<float>(), stream_of(ec)),
+           "gphl_sddmm_u_dot_v_f32_i32");
   return z;
 }
 
@@ -374,4 +436,6 @@ static auto registry =
         // additions with no counterpart in the reference's registry
         .op("my_ops::gsddmm_u_dot_v(Tensor x, Tensor y, int heads, " GRAPH_T " g) -> Tensor z", &u_dot_v)
         .op("my_ops::gat_fused(Tensor el, Tensor er, Tensor z, float slope, " GRAPH_T " g) -> Tensor y", &gat_fused)
-        .op("my_ops::SegmentMMEdgeSrc(Tensor x, Tensor y, " GRAPH_T " g) -> Tensor z", &SegmentMMEdgeSrc);
+        .op("my_ops::SegmentMMEdgeSrc(Tensor x, Tensor y, " GRAPH_T " g) -> Tensor z", &SegmentMMEdgeSrc)
+        .op("my_ops::gsddmm_e_dot_v(Tensor x, Tensor y, int heads, " GRAPH_T " g) -> Tensor z", &e_dot_v)
+        .op("my_ops::SpMMEdgeMul(Tensor x, Tensor y, " GRAPH_T " g) -> Tensor z", &SpMMEdgeMul);

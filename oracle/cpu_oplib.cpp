@@ -113,6 +113,37 @@ static Tensor segment_mm(const Tensor &x, const Tensor &w, const Tensor &pointer
 static Tensor SegmentMMNode(Tensor x, Tensor w, const G &g) { return segment_mm(x, w, g->ntype_pointer.value()); }
 static Tensor SegmentMMEdge(Tensor x, Tensor w, const G &g) { return segment_mm(x, w, g->etype_pointer.value()); }
 
+
+// ---- operators the reference does not register: the targets of the added fusion patterns, restated as the
+// unfused chains they replace so that a rewritten graph can be checked on the CPU -------------------------------
+static Tensor u_dot_v(Tensor l, Tensor r, int64_t heads, const G &g) {
+  auto a = two_d(l).index_select(0, g->COO_src), b = two_d(r).index_select(0, g->COO_dst);
+  return (a * b).reshape({a.size(0), heads, -1}).sum(2);
+}
+static Tensor e_dot_v(Tensor e, Tensor v, int64_t heads, const G &g) {
+  auto p = at::mul(e, v.index_select(0, g->COO_dst));
+  if (heads == 1) return p.sum({1}, true);
+  return p.reshape({p.size(0), heads, -1}).sum(2);
+}
+static Tensor SpMMEdgeMul(Tensor a, Tensor b, const G &g) {
+  std::vector<int64_t> dims{1};
+  auto a2 = two_d(a), b2 = two_d(b);
+  if (a2.size(1) != b2.size(1) && a2.size(1) > 1 && b2.size(1) > 1) {   // per-head weights
+    const bool a_is_w = a2.size(1) < b2.size(1);
+    const Tensor &x = a_is_w ? b2 : a2, &w = a_is_w ? a2 : b2;
+    const int64_t h = w.size(1);
+    return SpMMEdge((x.reshape({-1, h, x.size(1) / h}) * w.reshape({-1, h, 1})).reshape({-1, x.size(1)}), dims, false,
+                    c10::nullopt, g);
+  }
+  return SpMMEdge(at::mul(a, b), dims, false, c10::nullopt, g);
+}
+static Tensor gat_fused(Tensor el, Tensor er, Tensor z, double slope, const G &g) {
+  std::vector<int64_t> dims{1};
+  auto e = at::leaky_relu(u_add_v_mul_alpha(el, er, 1, g), slope);
+  return src_mul_e_sum(z, SegmentSoftmax(e, 1, c10::nullopt, g), dims, false, c10::nullopt, g);
+}
+static Tensor SegmentMMEdgeSrc(Tensor x, Tensor w, const G &g) { return SegmentMMEdge(BroadcastSrcNode(x, g), w, g); }
+
 #define GRAPH_T "__torch__.torch.classes.my_classes.DGLGraph"
 
 TORCH_LIBRARY(my_classes, m) {
@@ -143,4 +174,9 @@ static auto registry =
         .op("my_ops::gspmm_dst_mul_e_sum(Tensor x, Tensor y, int[] dim, bool k, int? t, " GRAPH_T " g) -> Tensor z",
             &dst_mul_e_sum)
         .op("my_ops::gsddmm_u_add_v_mul_alpha(Tensor x, Tensor y, int alpha," GRAPH_T " g) -> Tensor z",
-            &u_add_v_mul_alpha);
+            &u_add_v_mul_alpha)
+        .op("my_ops::gsddmm_u_dot_v(Tensor x, Tensor y, int heads, " GRAPH_T " g) -> Tensor z", &u_dot_v)
+        .op("my_ops::gsddmm_e_dot_v(Tensor x, Tensor y, int heads, " GRAPH_T " g) -> Tensor z", &e_dot_v)
+        .op("my_ops::SpMMEdgeMul(Tensor x, Tensor y, " GRAPH_T " g) -> Tensor z", &SpMMEdgeMul)
+        .op("my_ops::gat_fused(Tensor el, Tensor er, Tensor z, float slope, " GRAPH_T " g) -> Tensor y", &gat_fused)
+        .op("my_ops::SegmentMMEdgeSrc(Tensor x, Tensor y, " GRAPH_T " g) -> Tensor z", &SegmentMMEdgeSrc);
