@@ -184,30 +184,34 @@ __device__ __forceinline__ bool aligned16_dev(const void *p) { return (reinterpr
 __device__ __forceinline__ float leaky(float v, float slope) { return v >= 0.f ? v : v * slope; }
 
 // Online-softmax pair (running maximum, sum of exp(x - maximum)).
+// exp through the hardware base-2 exponential (ex2.approx after one multiplication).  Arguments here are
+// x - max <= 0: the relative error is about 2^-22 + |x| * 2^-24, under 2e-6 wherever the result is not
+// negligible, against an element tolerance of 1e-5 relative.  A quarter of the instructions of expf, which
+// bounded the softmax kernels.
+__device__ __forceinline__ float exp_neg(float x) { return __expf(x); }
+
 struct MaxSum {
   float m, s;
   __device__ __forceinline__ void init() {
     m = -INFINITY;
     s = 0.f;
   }
+  // reference point of the exponentials: the maximum, or 0 while everything seen is -inf (keeps inf - inf out)
+  static __device__ __forceinline__ float ref_of(float mx) { return mx == -INFINITY ? 0.f : mx; }
   __device__ __forceinline__ void push(float x) {
-    if (x > m) {
-      s = s * expf(m - x) + 1.f;  // m == -inf: s == 0, exp(-inf) == 0
-      m = x;
-    } else {
-      s += expf(x - m);
-    }
+    const float mn = fmaxf(m, x), r = ref_of(mn);
+    s = s * exp_neg(m - r) + exp_neg(x - r);
+    m = mn;
+  }
+  __device__ __forceinline__ void push4(float a, float b, float c, float d) {
+    const float mn = fmaxf(fmaxf(m, fmaxf(a, b)), fmaxf(c, d)), r = ref_of(mn);
+    s = s * exp_neg(m - r) + ((exp_neg(a - r) + exp_neg(b - r)) + (exp_neg(c - r) + exp_neg(d - r)));
+    m = mn;
   }
   __device__ __forceinline__ void merge(float om, float os) {
-    if (os == 0.f) return;
-    if (s == 0.f) {
-      m = om;
-      s = os;
-      return;
-    }
-    float mm = fmaxf(m, om);
-    s = s * expf(m - mm) + os * expf(om - mm);
-    m = mm;
+    const float mn = fmaxf(m, om), r = ref_of(mn);
+    s = s * exp_neg(m - r) + os * exp_neg(om - r);
+    m = mn;
   }
 };
 

@@ -67,7 +67,9 @@ extern "C" int gphl_plan_create(const int32_t *pointer, int64_t n_rows, int32_t 
     for (const Item &it : items) start[(size_t)(chunk - (it.end - it.begin)) + 1]++;
     for (size_t i = 1; i < start.size(); ++i) start[i] += start[i - 1];
     // buckets are ordered by falling length: the long items are those in front of the first short bucket
-    n_long = chunk > GPHL_SHORT_ITEM ? start[(size_t)(chunk - GPHL_SHORT_ITEM)] : 0;
+    int32_t short_item = GPHL_SHORT_ITEM;
+    if (const char *env = getenv("GPHL_SHORT_ITEM")) short_item = std::max(0, atoi(env));   // tuning knob
+    n_long = chunk > short_item ? start[(size_t)(chunk - short_item)] : 0;
     std::vector<Item> sorted(items.size());
     for (const Item &it : items) sorted[(size_t)start[(size_t)(chunk - (it.end - it.begin))]++] = it;
     items.swap(sorted);

@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(SW * 32) segment_stats_kernel(StatsArgs a) {
       for (; i + 3 * epw < it.end; i += 4 * epw) {        // four dependent index -> value chains in flight
         const HeadVec<V> v0 = logit(i), v1 = logit(i + epw), v2 = logit(i + 2 * epw), v3 = logit(i + 3 * epw);
 #pragma unroll
-        for (int v = 0; v < V; ++v) ms[v].push(v0.v[v]), ms[v].push(v1.v[v]), ms[v].push(v2.v[v]), ms[v].push(v3.v[v]);
+        for (int v = 0; v < V; ++v) ms[v].push4(v0.v[v], v1.v[v], v2.v[v], v3.v[v]);
       }
       for (; i < it.end; i += epw) {
         const HeadVec<V> v0 = logit(i);
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(SW * 32) segment_stats_kernel(StatsArgs a) {
     for (int v = 0; v < V; ++v) {
       float mr = ms[v].m;
       for (int off = a.Hp; off < 32; off <<= 1) mr = fmaxf(mr, __shfl_xor_sync(FULL, mr, off));
-      float sc = ms[v].s > 0.f ? ms[v].s * expf(ms[v].m - mr) : 0.f;
+      float sc = ms[v].s > 0.f ? ms[v].s * exp_neg(ms[v].m - mr) : 0.f;
       for (int off = a.Hp; off < 32; off <<= 1) sc += __shfl_xor_sync(FULL, sc, off);
       ms[v].m = mr, ms[v].s = sc;
     }
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(SW * 32) segment_stats_kernel(StatsArgs a) {
         const int eid = a.eidx ? __ldg(a.eidx + i) : i;
         HeadVec<V> y;
 #pragma unroll
-        for (int v = 0; v < V; ++v) y.v[v] = expf(x.v[v] - mx.v[v]) * inv.v[v];
+        for (int v = 0; v < V; ++v) y.v[v] = exp_neg(x.v[v] - mx.v[v]) * inv.v[v];
         store_heads<V>(a.y + (int64_t)eid * a.H + h, y);
       };
       int i = it.begin + eg;
@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(256) segment_stats_rows_kernel(StatsArgs a, in
   for (; i + 3 < it.end; i += 4) {
     const HeadVec<V> v0 = logit(i), v1 = logit(i + 1), v2 = logit(i + 2), v3 = logit(i + 3);
 #pragma unroll
-    for (int v = 0; v < V; ++v) ms[v].push(v0.v[v]), ms[v].push(v1.v[v]), ms[v].push(v2.v[v]), ms[v].push(v3.v[v]);
+    for (int v = 0; v < V; ++v) ms[v].push4(v0.v[v], v1.v[v], v2.v[v], v3.v[v]);
   }
   for (; i < it.end; ++i) {
     const HeadVec<V> v0 = logit(i);
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(256) segment_stats_rows_kernel(StatsArgs a, in
       const int eid = a.eidx ? __ldg(a.eidx + j) : j;
       HeadVec<V> y;
 #pragma unroll
-      for (int v = 0; v < V; ++v) y.v[v] = expf(x.v[v] - mx.v[v]) * inv.v[v];
+      for (int v = 0; v < V; ++v) y.v[v] = exp_neg(x.v[v] - mx.v[v]) * inv.v[v];
       store_heads<V>(a.y + (int64_t)eid * a.H + h, y);
     };
     i = it.begin;
@@ -224,38 +224,65 @@ __global__ void __launch_bounds__(256) segment_stats_rows_kernel(StatsArgs a, in
   }
 }
 
-__global__ void stats_merge_kernel(const int32_t *split_rows, const int32_t *split_ptr, int64_t n_split, int32_t H,
-                                   const float *scratch, float *stats) {
-  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= n_split * H) return;
-  const int64_t r = t / H;
-  const int h = (int)(t % H);
+// Combines the partial pairs of a cut row: one warp per (cut row, head), lanes striding over the row's pieces.
+__global__ void __launch_bounds__(256) stats_merge_kernel(const int32_t *split_rows, const int32_t *split_ptr,
+                                                         int64_t n_split, int32_t H, const float *scratch,
+                                                         float *stats) {
+  const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= n_split * H) return;
+  const int64_t r = w / H;
+  const int h = (int)(w % H);
   MaxSum ms;
   ms.init();
-  for (int s = split_ptr[r]; s < split_ptr[r + 1]; ++s) {
+  for (int s = split_ptr[r] + lane; s < split_ptr[r + 1]; s += 32) {
     const float2 p = reinterpret_cast<const float2 *>(scratch)[(int64_t)s * H + h];
     ms.merge(p.x, p.y);
   }
-  float2 o = ms.s > 0.f ? make_float2(ms.m, 1.f / ms.s) : make_float2(0.f, 0.f);
-  reinterpret_cast<float2 *>(stats)[(int64_t)split_rows[r] * H + h] = o;
+  float mr = ms.m;
+  for (int off = 1; off < 32; off <<= 1) mr = fmaxf(mr, __shfl_xor_sync(FULL, mr, off));
+  float sc = ms.s > 0.f ? ms.s * exp_neg(ms.m - mr) : 0.f;
+  for (int off = 1; off < 32; off <<= 1) sc += __shfl_xor_sync(FULL, sc, off);
+  if (lane == 0) {
+    float2 o = sc > 0.f ? make_float2(mr, 1.f / sc) : make_float2(0.f, 0.f);
+    reinterpret_cast<float2 *>(stats)[(int64_t)split_rows[r] * H + h] = o;
+  }
 }
 
-// Pass 2 for the cut rows (the others were finished by pass 1): one block per cut row.
+// Pass 2 for the cut rows (the others were finished by pass 1): one block per piece, so that a hub row of 10^5
+// positions is spread over hundreds of blocks.  Pieces of a cut row are `chunk` positions each (the last one
+// shorter) and their scratch slots are consecutive, so the slot number gives the row (search in split_ptr) and
+// the position range.
 template <int V>
-__global__ void __launch_bounds__(256) softmax_normalize_kernel(StatsArgs a, const int32_t *split_rows) {
-  const int row = __ldg(split_rows + blockIdx.x);
-  const int begin = __ldg(a.pointer + row), end = __ldg(a.pointer + row + 1);
+__global__ void __launch_bounds__(256) softmax_normalize_kernel(StatsArgs a, const int32_t *split_rows,
+                                                               const int32_t *split_ptr, int32_t n_split,
+                                                               int32_t chunk) {
+  __shared__ int s_row, s_begin, s_end;
+  if (threadIdx.x == 0) {
+    const int slot = blockIdx.x;
+    int lo = 0, hi = n_split - 1;                       // last r with split_ptr[r] <= slot
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (__ldg(split_ptr + mid) <= slot) lo = mid;
+      else hi = mid - 1;
+    }
+    const int row = __ldg(split_rows + lo);
+    const int begin = __ldg(a.pointer + row) + (slot - __ldg(split_ptr + lo)) * chunk;
+    s_row = row, s_begin = begin, s_end = min(begin + chunk, __ldg(a.pointer + row + 1));
+  }
+  __syncthreads();
+  const int row = s_row, begin = s_begin, end = s_end;
   const int units = a.H / V;
-  const int64_t total = (int64_t)(end - begin) * units;
-  for (int64_t t = threadIdx.x; t < total; t += blockDim.x) {
-    const int i = begin + (int)(t / units), h = (int)(t % units) * V;
+  const int total = (end - begin) * units;
+  for (int t = threadIdx.x; t < total; t += blockDim.x) {
+    const int i = begin + t / units, h = (t % units) * V;
     const int eid = a.eidx ? __ldg(a.eidx + i) : i;
     const HeadVec<V> x = load_heads<V>(a.x + (int64_t)eid * a.H + h);
     HeadVec<V> y;
 #pragma unroll
     for (int v = 0; v < V; ++v) {
       const float2 st = __ldg(reinterpret_cast<const float2 *>(a.stats) + (int64_t)row * a.H + h + v);
-      y.v[v] = expf(x.v[v] - st.x) * st.y;
+      y.v[v] = exp_neg(x.v[v] - st.x) * st.y;
     }
     store_heads<V>(a.y + (int64_t)eid * a.H + h, y);
   }
@@ -302,13 +329,18 @@ static int run_stats(const gphl_plan *plan, StatsArgs a, int64_t n_rows, cudaStr
     if (rc != GPHL_OK) return rc;
   }
   if (plan && plan->n_split_rows > 0) {
-    const int64_t total = plan->n_split_rows * a.H;
+    const int64_t total = plan->n_split_rows * a.H * 32;
     stats_merge_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(plan->split_rows, plan->split_ptr,
                                                                           plan->n_split_rows, a.H, plan->scratch, a.stats);
     rc = launched("stats_merge_kernel");
     if (rc != GPHL_OK || !NORMALIZE) return rc;
-    if (vec) softmax_normalize_kernel<4><<<(unsigned)plan->n_split_rows, 256, 0, stream>>>(a, plan->split_rows);
-    else softmax_normalize_kernel<1><<<(unsigned)plan->n_split_rows, 256, 0, stream>>>(a, plan->split_rows);
+    const unsigned pieces = (unsigned)plan->n_pieces;
+    if (vec)
+      softmax_normalize_kernel<4><<<pieces, 256, 0, stream>>>(a, plan->split_rows, plan->split_ptr,
+                                                               (int32_t)plan->n_split_rows, plan->chunk);
+    else
+      softmax_normalize_kernel<1><<<pieces, 256, 0, stream>>>(a, plan->split_rows, plan->split_ptr,
+                                                               (int32_t)plan->n_split_rows, plan->chunk);
     rc = launched("softmax_normalize_kernel");
   }
   return rc;

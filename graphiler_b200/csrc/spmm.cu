@@ -36,6 +36,7 @@ struct GatherArgs {
   float slope;
   int32_t relu;          // epilogue: max(., 0)
   int32_t exact;         // 1: compensated accumulation (default), 0: plain fp32 adds
+  int32_t wvec;          // per-head arrays (w | el, er, stats) can be read four heads at a time
   int32_t F, FV, H, DV;  // columns, 16-byte vectors per row, heads, vectors per head
 };
 
@@ -126,12 +127,37 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
       if (lane < n) {
         const int eid = a.eidx ? __ldg(a.eidx + base + lane) : base + lane;
         if (MODE == MUL_E) {
-          for (int h = 0; h < a.H; ++h) wsm[lane * a.H + h] = __ldg(a.w + (int64_t)eid * a.H + h);
+          if (a.wvec) {                                     // H % 4 == 0, 16-byte aligned arrays: four heads per access
+            for (int h = 0; h < a.H; h += 4)
+              *reinterpret_cast<float4 *>(wsm + lane * a.H + h) =
+                  __ldg(reinterpret_cast<const float4 *>(a.w + (int64_t)eid * a.H + h));
+          } else {
+            for (int h = 0; h < a.H; ++h) wsm[lane * a.H + h] = __ldg(a.w + (int64_t)eid * a.H + h);
+          }
+        } else if (a.wvec) {
+#pragma unroll 1
+          for (int h = 0; h < a.H; h += 4) {
+            const float4 el4 = __ldg(reinterpret_cast<const float4 *>(a.el + (int64_t)my_idx * a.H + h));
+            const float4 er4 = __ldg(reinterpret_cast<const float4 *>(a.er + (int64_t)it.row * a.H + h));
+            const float4 *st = reinterpret_cast<const float4 *>(a.stats + 2 * ((int64_t)it.row * a.H + h));
+            const float4 s01 = __ldg(st), s23 = __ldg(st + 1);       // (max, 1/sum) of heads h, h+1 | h+2, h+3
+            float4 wv;
+            wv.x = exp_neg(leaky(el4.x + er4.x, a.slope) - s01.x) * s01.y;
+            wv.y = exp_neg(leaky(el4.y + er4.y, a.slope) - s01.z) * s01.w;
+            wv.z = exp_neg(leaky(el4.z + er4.z, a.slope) - s23.x) * s23.y;
+            wv.w = exp_neg(leaky(el4.w + er4.w, a.slope) - s23.z) * s23.w;
+            *reinterpret_cast<float4 *>(wsm + lane * a.H + h) = wv;
+            if (a.alpha_out && blockIdx.y == 0) {
+              float *ao = a.alpha_out + (int64_t)eid * a.H + h;
+              ao[0] = wv.x, ao[1] = wv.y, ao[2] = wv.z, ao[3] = wv.w;
+            }
+          }
         } else {
+#pragma unroll 1
           for (int h = 0; h < a.H; ++h) {
             const float2 st = __ldg(reinterpret_cast<const float2 *>(a.stats) + (int64_t)it.row * a.H + h);
             float e = leaky(__ldg(a.el + (int64_t)my_idx * a.H + h) + __ldg(a.er + (int64_t)it.row * a.H + h), a.slope);
-            float wgt = expf(e - st.x) * st.y;
+            float wgt = exp_neg(e - st.x) * st.y;
             wsm[lane * a.H + h] = wgt;
             if (a.alpha_out && blockIdx.y == 0) a.alpha_out[(int64_t)eid * a.H + h] = wgt;
           }
@@ -443,7 +469,7 @@ __global__ void gather_sum_scalar_kernel(GatherArgs a, int32_t D) {
       if (MODE == MUL_E) {
         wgt = a.w[(int64_t)eid * a.H + h];
       } else {
-        wgt = expf(leaky(a.el[(int64_t)src * a.H + h] + erv, a.slope) - m) * inv;
+        wgt = exp_neg(leaky(a.el[(int64_t)src * a.H + h] + erv, a.slope) - m) * inv;
         if (a.alpha_out && f == h * D) a.alpha_out[(int64_t)eid * a.H + h] = wgt;
       }
       acc.fma_exact(v, wgt);
@@ -518,6 +544,9 @@ static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t
   if (vec_ok) {
     a.FV = a.F / VEC;
     a.DV = (MODE == COPY) ? a.FV : D / VEC;
+    a.wvec = 0;
+    if (MODE == MUL_E) a.wvec = a.H % 4 == 0 && aligned16(a.w);
+    if (MODE == GAT) a.wvec = a.H % 4 == 0 && aligned16(a.el) && aligned16(a.er) && aligned16(a.stats);
     static const bool use_bulk = [] {
       const char *e = getenv("GPHL_GATHER");
       return e && std::string(e) == "bulk";
