@@ -307,7 +307,8 @@ def segment_mm(x, w, type_pointer, gather_idx=None, out=None, row_scale=None, re
                tensor_cores: Optional[bool] = None, workspace=None):
     """y[p_t:p_{t+1}] = x[p_t:p_{t+1}] @ w[t] (rows of x optionally taken through ``gather_idx``), optionally followed
     by a per-row scale and relu.  ``tensor_cores``: None = use the tcgen05 kernel whenever the shape allows
-    (k % 4 == 0), True = require it, False = the exact-fp32 SIMT kernel."""
+    (k % 4 == 0) and the weights are not narrow (k <= 64 and n <= 32 go to the double-accumulating narrow kernel,
+    which is bound by the rows it moves), True = require it, False = the exact-fp32 SIMT kernels."""
     _dev(x, w, type_pointer, gather_idx, out, row_scale, workspace)
     m = gather_idx.numel() if gather_idx is not None else x.shape[0]
     t, k, n = w.shape
@@ -315,7 +316,8 @@ def segment_mm(x, w, type_pointer, gather_idx=None, out=None, row_scale=None, re
         raise GphlError("inner dimensions differ")
     y = out if out is not None else torch.empty((m, n), dtype=torch.float32, device=x.device)
     tc_ok = (k % 4 == 0) and x.data_ptr() % 16 == 0 and y.data_ptr() % 16 == 0
-    use_tc = tc_ok if tensor_cores is None else tensor_cores
+    narrow = k <= 64 and n <= 32
+    use_tc = (tc_ok and not narrow) if tensor_cores is None else tensor_cores
     if use_tc and not tc_ok:
         raise GphlError("the tensor-core kernel needs k % 4 == 0 and 16-byte aligned tensors")
     with torch.cuda.device(x.device):

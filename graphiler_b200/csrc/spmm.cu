@@ -37,6 +37,7 @@ struct GatherArgs {
   int32_t relu;          // epilogue: max(., 0)
   int32_t exact;         // 1: compensated accumulation (default), 0: plain fp32 adds
   int32_t wvec;          // per-head arrays (w | el, er, stats) can be read four heads at a time
+  int64_t n_long;        // items [0, n_long) are longer than GPHL_SHORT_ITEM positions; -1: unknown (no plan)
   int32_t F, FV, H, DV;  // columns, 16-byte vectors per row, heads, vectors per head
 };
 
@@ -269,6 +270,97 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
         hi[cv[v] * VEC + 2 * k] = h0, hi[cv[v] * VEC + 2 * k + 1] = h1;
         lo[cv[v] * VEC + 2 * k] = l0, lo[cv[v] * VEC + 2 * k + 1] = l1;
       }
+    }
+  }
+}
+
+// ---- short items of narrow features ----------------------------------------------------------------
+// Rows of at most 8 vectors (32 fp32 columns): a warp per item would leave most lanes idle on a low-degree row, so
+// LPR lanes take one item and a warp serves 32 / LPR items.  The lanes walk the item's positions in order, four rows in
+// flight, with no exchange between lanes.  The plan orders items by length, so the groups of a warp finish together.
+template <typename T, int LPR, int MODE, bool EXACT>
+__global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int64_t first_item) {
+  constexpr int VEC = VecOf<T>::N, VP = VEC / 2;
+  const int l = threadIdx.x % LPR;
+  const int64_t item_id = first_item + ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
+  if (item_id >= a.n_items) return;
+  const Item it = fetch_item(a.items, a.pointer, item_id);
+  const bool cok = l < a.FV;
+  const int cv = cok ? l : 0;
+  const int head = (MODE == COPY) ? 0 : cv / a.DV;
+  AccT<EXACT> acc[VP];
+#pragma unroll
+  for (int k = 0; k < VP; ++k) {
+    acc[k].hi = 0;
+    if constexpr (EXACT) acc[k].lo = 0;
+  }
+  float erv = 0.f, mx = 0.f, inv = 0.f;
+  if (MODE == GAT) {
+    erv = __ldg(a.er + (int64_t)it.row * a.H + head);
+    const float2 st = __ldg(reinterpret_cast<const float2 *>(a.stats) + (int64_t)it.row * a.H + head);
+    mx = st.x, inv = st.y;
+  }
+  const uint4 *x = static_cast<const uint4 *>(a.x);
+  auto weight = [&](int i, int src) {
+    if (MODE == MUL_E) {
+      const int eid = a.eidx ? __ldg(a.eidx + i) : i;
+      return __ldg(a.w + (int64_t)eid * a.H + head);
+    }
+    return exp_neg(leaky(__ldg(a.el + (int64_t)src * a.H + head) + erv, a.slope) - mx) * inv;
+  };
+  auto accumulate = [&](const uint4 &raw, float wgt) {
+    uint64_t val[VP];
+    unpack_pairs<T>(raw, val);
+    const uint64_t w2 = pack2(wgt, wgt);
+#pragma unroll
+    for (int k = 0; k < VP; ++k) {
+      if (MODE == COPY) acc[k].add(val[k]);
+      else if (MODE == GAT) acc[k].add(fmul2(val[k], w2));
+      else acc[k].fma_exact(val[k], w2);
+    }
+  };
+  int i = it.begin;
+  for (; i + 3 < it.end; i += 4) {
+    int src[4];
+    uint4 raw[4];
+    float wgt[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) src[u] = __ldg(a.idx + i + u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) raw[u] = __ldg(x + (int64_t)src[u] * a.FV + cv);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) wgt[u] = (MODE == COPY) ? 1.f : weight(i + u, src[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) accumulate(raw[u], wgt[u]);
+  }
+  for (; i < it.end; ++i) {
+    const int src = __ldg(a.idx + i);
+    const uint4 raw = __ldg(x + (int64_t)src * a.FV + cv);
+    accumulate(raw, (MODE == COPY) ? 1.f : weight(i, src));
+  }
+  if (!cok) return;
+  if (it.slot < 0) {
+    T *y = static_cast<T *>(a.y) + (int64_t)it.row * a.F;
+    const float scale = a.dst_scale ? __ldg(a.dst_scale + it.row) : 1.f;
+    float o[VEC];
+#pragma unroll
+    for (int k = 0; k < VP; ++k) unpack2(acc[k].value(), o[2 * k], o[2 * k + 1]);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
+      if (a.relu) o[k] = fmaxf(o[k], 0.f);
+    }
+    VecOf<T>::store(y + (int64_t)cv * VEC, o);
+  } else {
+    float *hi = a.scratch + (int64_t)(2 * it.slot) * a.plane;
+    float *lo = hi + a.plane;
+#pragma unroll
+    for (int k = 0; k < VP; ++k) {
+      float h0, h1, l0, l1;
+      unpack2(acc[k].hi, h0, h1);
+      unpack2(acc[k].lo, l0, l1);
+      hi[cv * VEC + 2 * k] = h0, hi[cv * VEC + 2 * k + 1] = h1;
+      lo[cv * VEC + 2 * k] = l0, lo[cv * VEC + 2 * k + 1] = l1;
     }
   }
 }
@@ -518,10 +610,32 @@ static int launch_vec_e(const GatherArgs &a, cudaStream_t stream) {
   return launched("gather_sum_kernel");
 }
 
+template <typename T, int MODE, int LPR, bool EXACT>
+static int launch_rows_e(const GatherArgs &a, int64_t first_item, cudaStream_t stream) {
+  const int64_t threads = (a.n_items - first_item) * LPR;
+  gather_sum_rows_kernel<T, LPR, MODE, EXACT><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(a, first_item);
+  return launched("gather_sum_rows_kernel");
+}
+
+// Narrow rows (FV <= LPR <= 8): the first n_long items (the long ones) go a warp each, the short ones a lane group each.
 template <typename T, int MODE, int LPR, int NV>
 static int launch_vec(const GatherArgs &a, cudaStream_t stream) {
   // plain accumulation is offered for the unweighted sum and the fused attention aggregate
-  if (MODE != MUL_E && !a.exact) return launch_vec_e<T, MODE, LPR, NV, false>(a, stream);
+  const bool exact = !(MODE != MUL_E && !a.exact);
+  if constexpr (LPR <= 8 && NV == 1) {
+    if (a.n_long >= 0 && a.n_long < a.n_items && !(MODE == GAT && a.alpha_out)) {
+      int rc = GPHL_OK;
+      if (a.n_long > 0) {
+        GatherArgs w = a;
+        w.n_items = a.n_long;
+        rc = exact ? launch_vec_e<T, MODE, LPR, NV, true>(w, stream) : launch_vec_e<T, MODE, LPR, NV, false>(w, stream);
+        if (rc != GPHL_OK) return rc;
+      }
+      return exact ? launch_rows_e<T, MODE, LPR, true>(a, a.n_long, stream)
+                   : launch_rows_e<T, MODE, LPR, false>(a, a.n_long, stream);
+    }
+  }
+  if (!exact) return launch_vec_e<T, MODE, LPR, NV, false>(a, stream);
   return launch_vec_e<T, MODE, LPR, NV, true>(a, stream);
 }
 
@@ -529,9 +643,11 @@ template <typename T, int MODE>
 static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t stream) {
   constexpr int VEC = VecOf<T>::N;
   if (a.n_items == 0 || a.F == 0) return GPHL_OK;
+  a.n_long = -1;
   if (plan) {
     a.items = plan->items;
     a.n_items = plan->n_items;
+    a.n_long = plan->n_long_items;
     a.scratch = plan->scratch;
     a.plane = plan->max_feat;
     if (plan->n_pieces > 0 && a.F > plan->max_feat)

@@ -368,7 +368,9 @@ Tensor segment_mm(const Tensor &x, const Tensor &w, const c10::optional<Tensor> 
   if (gather.has_value()) gi = cuda_idx(gather.value(), torch::kInt64, "gather index");
   c10::cuda::CUDAGuard guard(xc.device());
   const int64_t k = xc.size(1), n = wc.size(2);
-  const bool tc = (k % 4 == 0) && (reinterpret_cast<uintptr_t>(xc.data_ptr()) % 16 == 0) &&
+  // narrow weights (k <= 64, n <= 32) take the double-accumulating SIMT kernel: a 128-row tensor-core tile would be
+  // mostly padding there
+  const bool tc = (k % 4 == 0) && !(k <= 64 && n <= 32) && (reinterpret_cast<uintptr_t>(xc.data_ptr()) % 16 == 0) &&
                   (reinterpret_cast<uintptr_t>(y.data_ptr()) % 16 == 0);
   if (tc) {
     // tensor-core path: the split weights live in a scratch tensor from the caching allocator

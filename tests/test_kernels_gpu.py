@@ -146,7 +146,8 @@ def test_spmm_copy_u_sum_bf16(graph, feat):
     close(y, truth, rtol=2.0 ** -8, atol=1e-6)
 
 
-@pytest.mark.parametrize("heads,dim", [(1, 64), (8, 8), (8, 32), (1, 1), (4, 3), (2, 20), (1, 256)])
+@pytest.mark.parametrize("heads,dim", [(1, 64), (8, 8), (8, 32), (1, 1), (4, 3), (2, 20), (1, 256), (2, 8), (1, 32), (8, 4),
+                                       (1, 4)])
 @pytest.mark.parametrize("side", ["src", "dst"])
 def test_spmm_u_mul_e_sum(graph, heads, dim, side):
     g = graph.to(DEV)
@@ -206,7 +207,7 @@ def test_segment_softmax_all_negative_and_huge_logits():
     close(y, O.segment_softmax(x, graph.in_pointer, graph.in_edge_indices))
 
 
-@pytest.mark.parametrize("heads,dim", [(8, 8), (8, 32), (1, 64), (2, 3), (1, 1)])
+@pytest.mark.parametrize("heads,dim", [(8, 8), (8, 32), (1, 64), (2, 3), (1, 1), (2, 8), (4, 4), (1, 16)])
 @pytest.mark.parametrize("use_plan", [False, True])
 def test_gat_fused(graph, heads, dim, use_plan):
     g = graph.to(DEV)
@@ -220,6 +221,8 @@ def test_gat_fused(graph, heads, dim, use_plan):
                                 return_alpha=True)
     close(out, truth)
     close(alpha, talpha)
+    # without the attention weights as an output (narrow rows then take the lane-group kernel)
+    close(capi.gat_fused(g.in_pointer, g.in_node_indices, g.in_edge_indices, el, er, z, 0.2, plan), truth)
     # unfused sequence gives the same numbers within the same tolerance
     e = capi.sddmm_u_add_v(g.COO_src, g.COO_dst, el, er)
     e = torch.nn.functional.leaky_relu(e, 0.2)
@@ -266,7 +269,8 @@ def test_broadcasts_bit_exact(dtype, shape):
     assert torch.equal(capi.gather_rows(g.etype_COO, xe), xe[g.etype_COO])
 
 
-@pytest.mark.parametrize("k,n", [(16, 16), (128, 128), (20, 7), (1, 1), (64, 200), (256, 256), (100, 40)])
+@pytest.mark.parametrize("k,n", [(16, 16), (128, 128), (20, 7), (1, 1), (64, 200), (256, 256), (100, 40), (64, 32), (33, 30),
+                                 (65, 32)])
 @pytest.mark.parametrize("tensor_cores", [False, True])
 def test_segment_mm(k, n, tensor_cores):
     if tensor_cores and k % 4:
