@@ -34,6 +34,16 @@ __global__ void u_add_v_scalar_kernel(const I *__restrict__ src, const I *__rest
   }
 }
 
+// The two halves of a packed accumulator as one compensated value.
+__device__ __forceinline__ Acc join_halves(const Acc2 &p) {
+  float h0, h1, l0, l1;
+  unpack2(p.hi, h0, h1);
+  unpack2(p.lo, l0, l1);
+  Acc r{h0, l0};
+  r.merge(h1, l1);
+  return r;
+}
+
 template <typename I, bool VEC4>
 __global__ void u_dot_v_kernel(const I *__restrict__ src, const I *__restrict__ dst, int64_t n_edges, int32_t H,
                                int32_t D, const float *__restrict__ l, const float *__restrict__ r,
@@ -44,26 +54,28 @@ __global__ void u_dot_v_kernel(const I *__restrict__ src, const I *__restrict__ 
     const int h = (int)(t - e * H);
     const float *a = l + ((int64_t)__ldg(src + e) * H + h) * D;
     const float *b = r + ((int64_t)__ldg(dst + e) * H + h) * D;
-    Acc acc{0.f, 0.f};
     if (VEC4) {
+      // even and odd elements in the two halves of a packed accumulator, joined at the end
+      Acc2 acc2{0, 0};
       for (int d = 0; d < D; d += 4) {
         const float4 p = __ldg(reinterpret_cast<const float4 *>(a + d));
         const float4 q = __ldg(reinterpret_cast<const float4 *>(b + d));
-        acc.fma_exact(p.x, q.x);
-        acc.fma_exact(p.y, q.y);
-        acc.fma_exact(p.z, q.z);
-        acc.fma_exact(p.w, q.w);
+        acc2.fma_exact(pack2(p.x, p.y), pack2(q.x, q.y));
+        acc2.fma_exact(pack2(p.z, p.w), pack2(q.z, q.w));
       }
+      z[t] = join_halves(acc2).value();
     } else {
+      Acc acc{0.f, 0.f};
       for (int d = 0; d < D; ++d) acc.fma_exact(__ldg(a + d), __ldg(b + d));
+      z[t] = acc.value();
     }
-    z[t] = acc.value();
   }
 }
 
-// u_dot_v with coalesced row reads: a sub-warp group of LPR lanes reads one edge's two endpoint rows as
-// consecutive 16-byte vectors (the same lane layout as the row-gather SpMM), multiplies exactly, and the DV = D / 4
-// lanes that share a head reduce with shuffles.  32 / LPR edges are in flight per warp instruction, U per group.
+// u_dot_v with coalesced row reads: a sub-warp group of LPR lanes reads one edge's two endpoint rows, NV consecutive
+// 16-byte vectors per lane (all of one head: NV divides the DV = D / 4 vectors of a head), multiplies exactly in
+// packed pairs, and the DV / NV lanes that share a head reduce with shuffles.  32 / LPR edges are in flight per
+// warp instruction, U per group.
 template <typename I, int LPR, int NV>
 __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__ src, const I *__restrict__ dst,
                                                            int64_t n_edges, int32_t H, int32_t FV, int32_t DV,
@@ -71,6 +83,9 @@ __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__
                                                            float *__restrict__ z) {
   constexpr int G = 32 / LPR, U = (NV >= 2) ? 2 : 4;
   const int lane = threadIdx.x & 31, g = lane / LPR, ll = lane % LPR;
+  const int cv0 = ll * NV;                                   // first vector of this lane
+  const bool cok = cv0 < FV;                                 // FV is a multiple of NV: all or none of the lane's vectors
+  const int lanes_per_head = DV / NV;
   const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   for (int64_t base = warp_id * 32; base < n_edges; base += n_warps * 32) {
@@ -85,28 +100,27 @@ __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__
       for (int u = 0; u < U; ++u) {
         e[u] = jj + u * G + g;
         const int64_t s_row = __shfl_sync(FULL, my_s, e[u] & 31), d_row = __shfl_sync(FULL, my_d, e[u] & 31);
+        const bool ok = e[u] < n && cok;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          const int cv = v * LPR + ll;
-          const bool ok = e[u] < n && cv < FV;
-          a[u][v] = ok ? __ldg(l + s_row * FV + cv) : make_float4(0.f, 0.f, 0.f, 0.f);
-          b[u][v] = ok ? __ldg(r + d_row * FV + cv) : make_float4(0.f, 0.f, 0.f, 0.f);
+          a[u][v] = ok ? __ldg(l + s_row * FV + cv0 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+          b[u][v] = ok ? __ldg(r + d_row * FV + cv0 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
+        Acc2 acc2{0, 0};
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          Acc acc{0.f, 0.f};
-          acc.fma_exact(a[u][v].x, b[u][v].x), acc.fma_exact(a[u][v].y, b[u][v].y);
-          acc.fma_exact(a[u][v].z, b[u][v].z), acc.fma_exact(a[u][v].w, b[u][v].w);
-          for (int off = 1; off < DV; off <<= 1) {            // DV is a power of two <= LPR
-            const float ohi = __shfl_xor_sync(FULL, acc.hi, off), olo = __shfl_xor_sync(FULL, acc.lo, off);
-            acc.merge(ohi, olo);
-          }
-          const int cv = v * LPR + ll;
-          if (e[u] < n && cv < FV && (cv % DV) == 0) z[(base + e[u]) * H + cv / DV] = acc.value();
+          acc2.fma_exact(pack2(a[u][v].x, a[u][v].y), pack2(b[u][v].x, b[u][v].y));
+          acc2.fma_exact(pack2(a[u][v].z, a[u][v].w), pack2(b[u][v].z, b[u][v].w));
         }
+        Acc acc = join_halves(acc2);
+        for (int off = 1; off < lanes_per_head; off <<= 1) {   // a power of two <= LPR
+          const float ohi = __shfl_xor_sync(FULL, acc.hi, off), olo = __shfl_xor_sync(FULL, acc.lo, off);
+          acc.merge(ohi, olo);
+        }
+        if (e[u] < n && cok && (ll % lanes_per_head) == 0) z[(base + e[u]) * H + cv0 / DV] = acc.value();
       }
     }
   }
@@ -162,7 +176,8 @@ static int u_dot_v(const I *src, const I *dst, int64_t n_edges, int64_t heads, i
     // kernel below is faster, its reads are still sector-sized): whole rows as 16-byte vectors, heads reduced
     // across lanes
     const int64_t lpr = fv <= 1 ? 1 : fv <= 2 ? 2 : fv <= 4 ? 4 : fv <= 8 ? 8 : fv <= 16 ? 16 : 32;
-    if (dv <= lpr) {
+    const int64_t nv = fv <= 32 ? 1 : fv <= 64 ? 2 : 4;       // vectors per lane; a lane must stay inside one head
+    if (dv % nv == 0 && dv / nv <= lpr) {
       switch (lpr) {
         case 1: return launch_u_dot_v_rows<I, 1, 1>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);
         case 2: return launch_u_dot_v_rows<I, 2, 1>(src, dst, n_edges, heads, fv, dv, l, r, z, stream);

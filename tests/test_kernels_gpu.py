@@ -176,7 +176,7 @@ def test_sddmm_u_add_v(graph, feat, idx_dtype):
     close(z, O.sddmm_u_add_v(l, r, graph.COO_src, graph.COO_dst))
 
 
-@pytest.mark.parametrize("heads,dim", [(8, 16), (1, 64), (3, 5), (8, 1), (8, 32), (4, 128), (2, 64)])
+@pytest.mark.parametrize("heads,dim", [(8, 16), (1, 64), (3, 5), (8, 1), (8, 32), (4, 128), (2, 64), (64, 4), (32, 8), (16, 16)])
 def test_sddmm_u_dot_v(graph, heads, dim):
     g = graph.to(DEV)
     l = torch.randn(g.num_nodes, heads * dim, device=DEV)
