@@ -475,6 +475,10 @@ def run_native(args):
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
             # one-pass ncu capture summarised in profiles/gather_sum_copy_u_sum_f256.md
             line["roofline"]["traffic"] = {"fp32": 28.15e9 + 2.55e9, "bf16": 10.23e9 + 1.33e9}[args.dtype]
+            # the same launch seen from DRAM: bytes actually moved / kernel time, against the same peak (the gather
+            # re-reads a source row once per edge; what L2 does not absorb is DRAM traffic the kernel cannot avoid)
+            line["roofline"]["traffic_gbs"] = line["roofline"]["traffic"] / k_ms_max / 1e6
+            line["roofline"]["traffic_frac"] = line["roofline"]["traffic_gbs"] / hbm
     if g_cpu is not None:
         threads = os.cpu_count() or 1
         target = max(1000, int(e * args.cpu_fraction))
