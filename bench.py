@@ -168,7 +168,8 @@ def workload_config(g, args, world):
             "nodes": g.num_nodes, "edges_incl_self_loops": g.num_edges, "feat": 256, "scale": args.scale,
             "storage": args.dtype, "accumulation": "fp32 plain" if getattr(args, "fast_accum", False) else "fp32 compensated (two-sum)",
             "partition": ("none" if world == 1 else f"dst-rows x{world} (edge-balanced) + all-gather in {args.gather_chunks} overlapped pieces"
-                          if args.exchange == "allgather" else f"dst-rows x{world} (edge-balanced) + halo all-to-all of the rows each shard reads"),
+                          if args.exchange == "allgather" else f"dst-rows x{world} (edge-balanced) + halo all-to-all of the rows each shard reads, source rows "
+                          + ("dealt to the ranks by a hash of their id" if args.ownership != "blocks" else "owned in contiguous blocks")),
             "l2": "inputs (2.4 GB features, 0.25 GB indices) exceed the 126 MB L2; no flush between steps"}
 
 
@@ -323,10 +324,11 @@ def run_native(args):
     norm = g.in_degrees().clamp(min=1).to(torch.float32).pow(-0.5).unsqueeze(1)
 
     sl = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, feat, dtype=dtype, rank=rank, world=world,
-                            chunks=args.gather_chunks, exchange=args.exchange)
-    lo, hi = sl.block_range
+                            chunks=args.gather_chunks, exchange=args.exchange,
+                            ownership=(args.ownership if args.exchange == "halo" and args.ownership != "auto" else None))
+    own = sl.owned_rows                              # source rows this rank projects (a block, or dealt by hash)
     r0, r1 = sl.shard.row0, sl.shard.row1
-    x_blk, nsrc_blk, ndst_loc = x[lo:hi].contiguous(), norm[lo:hi].contiguous(), norm[r0:r1].contiguous()
+    x_blk, nsrc_blk, ndst_loc = x[own].contiguous(), norm[own].contiguous(), norm[r0:r1].contiguous()
     ndst_vec = ndst_loc.reshape(-1).contiguous()
     g_cpu = g.to("cpu") if (rank == 0 and world == 1 and not args.no_cpu) else None
     x_cpu = x.cpu() if g_cpu is not None else None
@@ -362,6 +364,8 @@ def run_native(args):
         step()
     sync()
     kev.clear()
+    if world > 1 and args.exchange == "halo":
+        sl.phase_marks = []
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -384,6 +388,24 @@ def run_native(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, k_ms_max = float(t[0]), float(t[1])
+    phases = None
+    if getattr(sl, "phase_marks", None):
+        # where a step's time goes on the slowest rank of each phase: projection, packing of the requested rows,
+        # all-to-all (includes waiting for the slowest sender), aggregation
+        marks, sl.phase_marks = sl.phase_marks, None
+        acc = {}
+        for (n0, e0), (n1, e1) in zip(marks, marks[1:]):
+            if n1 != "start":
+                acc[n1] = acc.get(n1, 0.0) + e0.elapsed_time(e1)
+        names = ["project", "pack", "exchange"]
+        pt = torch.tensor([acc.get(k, 0.0) / args.steps for k in names], device=dev, dtype=torch.float64)
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        phases = {k: float(v) for k, v in zip(names, pt)}
+        phases["aggregate"] = k_ms_max
+        phases["halo_rows"] = int(sl.halo_rows)
+        sent = torch.tensor([sl.send_rows.numel(), -sl.send_rows.numel()], device=dev, dtype=torch.int64)
+        dist.all_reduce(sent, op=dist.ReduceOp.MAX)
+        phases["rows_sent_max_over_ranks"], phases["rows_sent_min_over_ranks"] = int(sent[0]), int(-sent[1])
 
     # end to end: node features from pinned host memory every step, result back to the host
     x_host = x_blk.cpu().pin_memory()
@@ -471,6 +493,8 @@ def run_native(args):
                         "serial_ms": e2e_serial_ms, "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * world,
                         "d2h_bytes_per_step": n * feat * out.element_size()},
                 "gpu_launches": int(launches), "clocks": clocks}
+        if phases is not None:
+            line["phases_ms"] = phases
         if world == 1 and args.scale == 1.0:
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
             # one-pass ncu capture summarised in profiles/gather_sum_copy_u_sum_f256.md
@@ -510,6 +534,8 @@ def main():
     ap.add_argument("--cpu-fraction", type=float, default=1.0 / 64, help="share of the edges in the CPU sample")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-config layer timings")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--ownership", default="auto", choices=["auto", "blocks", "hashed"],
+                    help="halo exchange: which rank projects which source rows (auto = hashed)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "halo"],
                     help="N > 1: all-gather every projected row, or send each shard only the rows it reads (all-to-all); "
                          "auto = halo from 4 GPUs up (measured: 3.9 vs 5.1 ms at 8, 5.4 vs 5.5 at 4, 7.9 vs 6.8 at 2)")

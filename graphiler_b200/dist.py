@@ -9,6 +9,10 @@ to-do); this module is new functionality.  One process per GPU:
 * the dense projection is balanced by rows instead: rank p projects the equal-sized block
   ``[p*B, (p+1)*B)`` of source nodes, and one NCCL all-gather over NVLink assembles the full
   source-feature matrix in each GPU's own memory; kernels then read local memory only;
+* or (``exchange="halo"``) every rank receives only the source rows its shard reads, through one all-to-all;
+  source rows are then dealt to the ranks by a hash of their id (``owned_rows``), because on a power-law
+  graph whose popular nodes have neighbouring ids a contiguous block would make one rank the sender of most
+  of the traffic;
 * the row-split plan of a shard depends only on each row's own length, so concatenating the
   shards' outputs in rank order reproduces the single-GPU result bit for bit.
 """
@@ -73,7 +77,7 @@ class ShardedLayer:
 
     def __init__(self, in_pointer, in_node_indices, num_nodes: int, feat: int, dtype=torch.float32,
                  rank: Optional[int] = None, world: Optional[int] = None, group=None, make_plan: bool = True,
-                 chunks: int = 1, exchange: str = "allgather"):
+                 chunks: int = 1, exchange: str = "allgather", ownership: Optional[str] = None):
         self.group = group
         self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
@@ -87,6 +91,7 @@ class ShardedLayer:
         if exchange not in ("allgather", "halo"):
             raise ValueError("exchange must be 'allgather' or 'halo'")
         self.exchange = exchange if self.world > 1 else "allgather"
+        self.phase_marks = None         # set to a list to have the halo path append (name, CUDA event) after each phase
         if self.exchange == "halo":
             chunks = 1
         self.chunks = max(1, int(chunks)) if self.world > 1 else 1
@@ -98,6 +103,12 @@ class ShardedLayer:
             pos = ((o // self.chunk_rows) * self.world + r) * self.chunk_rows + o % self.chunk_rows
             self.shard.node_indices = pos.to(torch.int32)
         dev = in_pointer.device
+        # which rank projects which source rows: contiguous equal blocks, or (halo default) dealt by a hash of the id
+        self.ownership = ownership or ("hashed" if self.exchange == "halo" else "blocks")
+        if self.ownership not in ("blocks", "hashed") or (self.ownership == "hashed" and self.exchange != "halo"):
+            raise ValueError("ownership must be 'blocks', or 'hashed' together with exchange='halo'")
+        lo = min(num_nodes, self.rank * self.block)
+        self.owned_rows = torch.arange(lo, min(num_nodes, lo + self.block), dtype=torch.int64, device=dev)
         if self.exchange == "halo":
             self._setup_halo(feat, dtype, dev)
             self._extra = {}
@@ -120,28 +131,50 @@ class ShardedLayer:
         once which of the owner's rows it needs, and each step the owners pack exactly those rows and one
         all-to-all delivers them into a compact buffer.  The shard's indices are renumbered to that buffer; the
         values and their order are unchanged, so results stay bit-identical to the single-GPU layer."""
-        needed = torch.unique(self.shard.node_indices.to(torch.int64))             # sorted: grouped by owner block
-        owner = needed // self.block
-        need_counts = torch.bincount(owner, minlength=self.world)
+        n, world = self.num_nodes, self.world
+        ids = torch.arange(n, dtype=torch.int64, device=dev)
+        if self.ownership == "hashed":
+            owner_of = (((ids * 2654435761) & 0xFFFFFFFF) >> 13) % world           # multiplicative hash of the row id
+        else:
+            owner_of = ids // self.block
+        order = torch.argsort(owner_of, stable=True)                               # rows grouped by owner, ascending id
+        counts = torch.bincount(owner_of, minlength=world)
+        offsets = torch.cumsum(counts, 0) - counts
+        local_of = torch.empty(n, dtype=torch.int64, device=dev)                   # position of a row in its owner's block
+        local_of[order] = ids - offsets[owner_of[order]]
+        o0, c0 = int(offsets[self.rank]), int(counts[self.rank])
+        self.owned_rows = order[o0:o0 + c0].contiguous()
+        idx64 = self.shard.node_indices.to(torch.int64)
+        needed = torch.unique(idx64)
+        keys, perm = torch.sort(owner_of[needed] * n + needed)                     # requests grouped by owner, then by id
+        needed = needed[perm]
+        need_counts = torch.bincount(owner_of[needed], minlength=world)
         self.recv_counts = need_counts.tolist()
         send_counts = torch.empty_like(need_counts)
         dist.all_to_all_single(send_counts, need_counts, group=self.group)
         self.send_counts = send_counts.tolist()
-        ask = (needed - owner * self.block).contiguous()                          # block-relative row of each request
+        ask = local_of[needed].contiguous()                                        # owner-relative row of each request
         asked = torch.empty(int(sum(self.send_counts)), dtype=torch.int64, device=dev)
         dist.all_to_all_single(asked, ask, output_split_sizes=self.send_counts, input_split_sizes=self.recv_counts,
                                group=self.group)
         self.send_rows = asked                                                    # rows of my block, grouped by requester
-        self.shard.node_indices = torch.searchsorted(needed, self.shard.node_indices.to(torch.int64)).to(torch.int32)
-        self.proj = torch.zeros((self.block, feat), dtype=dtype, device=dev)       # my projected block
+        self.shard.node_indices = torch.searchsorted(keys, owner_of[idx64] * n + idx64).to(torch.int32)
+        self.proj = torch.zeros((c0, feat), dtype=dtype, device=dev)               # my projected rows
         self.send_buf = torch.empty((asked.numel(), feat), dtype=dtype, device=dev)
         self.gathered = torch.empty((needed.numel(), feat), dtype=dtype, device=dev)   # compact: only the rows this shard reads
         self.halo_rows = int(needed.numel())
 
     @property
     def block_range(self):
+        """(lo, hi) of this rank's contiguous source block (``ownership == 'blocks'``); see ``owned_rows``."""
+        if self.ownership != "blocks":
+            raise ValueError("source rows are dealt by hash: use owned_rows")
         lo = self.rank * self.block
         return lo, min(self.num_nodes, lo + self.block)
+
+    @property
+    def num_owned(self) -> int:
+        return int(self.owned_rows.numel())
 
     def my_block(self) -> torch.Tensor:
         """View of this rank's slot in the gather buffer: write the projected rows here (chunks == 1 only)."""
@@ -159,17 +192,20 @@ class ShardedLayer:
         """Produce this rank's source rows and assemble everyone's.  ``fill(row_lo, row_hi, out)`` writes rows
         [row_lo, row_hi) of this rank's block (block-relative) into ``out``.  Piece by piece: the collective of a
         piece is issued asynchronously right after its rows were produced and overlaps the next piece's ``fill``."""
-        lo, hi = self.block_range
-        n_mine = hi - lo
+        n_mine = self.num_owned
         if self.exchange == "halo":
+            self._mark("start")
             fill(0, n_mine, self.proj[:n_mine])
+            self._mark("project")
             if self.proj.is_cuda:
                 from . import capi
                 capi.gather_rows(self.send_rows, self.proj, out=self.send_buf)    # pack the requested rows
             else:
                 torch.index_select(self.proj, 0, self.send_rows, out=self.send_buf)
+            self._mark("pack")
             dist.all_to_all_single(self.gathered, self.send_buf, output_split_sizes=self.recv_counts,
                                    input_split_sizes=self.send_counts, group=self.group)
+            self._mark("exchange")
             return self.gathered
         works = []
         for c in range(self.chunks):
@@ -183,6 +219,12 @@ class ShardedLayer:
         for w in works:
             w.wait()
         return self.gathered
+
+    def _mark(self, name: str):
+        if self.phase_marks is not None and self.proj.is_cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_marks.append((name, ev))
 
     def extra_buffer(self, name: str, width: int, dtype=None) -> torch.Tensor:
         """A further persistent (world*block, width) gather buffer (attention logits of the GAT layer); float32
@@ -217,7 +259,7 @@ class ShardedLayer:
 def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, norm_src_block, norm_dst_local,
                       relu: bool = True, aggregate: Optional[Callable] = None):
     """One GCN layer on this rank: project the local source block, all-gather, aggregate the local
-    destination rows.  ``feature_block`` holds rows ``sl.block_range`` of the node features."""
+    destination rows.  ``feature_block`` holds rows ``sl.owned_rows`` of the node features."""
     def fill(r0, r1, out):
         if feature_block.is_cuda:
             from .layers import project

@@ -45,15 +45,17 @@ def _worker(rank, world, port, tmp):
 
     fulls = []
     # one collective per layer, three overlapped pieces, or the sparse (halo) exchange of only the rows a shard reads
-    for chunks, exchange in ((1, "allgather"), (3, "allgather"), (1, "halo")):
+    for chunks, exchange, ownership in ((1, "allgather", None), (3, "allgather", None), (1, "halo", None),
+                                        (1, "halo", "blocks")):
         sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], dtype=torch.float64,
-                             rank=rank, world=world, make_plan=False, chunks=chunks, exchange=exchange)
-        lo, hi = sl.block_range
+                             rank=rank, world=world, make_plan=False, chunks=chunks, exchange=exchange,
+                             ownership=ownership)
+        own = sl.owned_rows                       # a contiguous block, or (halo) rows dealt by a hash of their id
         r0, r1 = sl.shard.row0, sl.shard.row1
-        y = gd.gcn_layer_sharded(sl, x[lo:hi], w, norm[lo:hi], norm[r0:r1], aggregate=aggregate)
+        y = gd.gcn_layer_sharded(sl, x[own], w, norm[own], norm[r0:r1], aggregate=aggregate)
         fulls.append(sl.gather_outputs(y))
     full = fulls[0]
-    assert torch.equal(fulls[0], fulls[1]) and torch.equal(fulls[0], fulls[2])
+    assert all(torch.equal(fulls[0], f) for f in fulls[1:])
     # GAT: z, el and er are gathered; the fused operator runs on the local destination rows
     c1 = synthetic.make_c1(scale=0.02)
     g1, p1 = c1.graph, {k: v.double() for k, v in c1.params.items()}

@@ -37,8 +37,8 @@ def _worker(rank, world, port, tmp):
     full4 = s4.gather_outputs(y4)
     # and with the sparse (halo) exchange: only the source rows a shard reads travel, through one all-to-all
     sh = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, exchange="halo")
-    loh, hih = sh.block_range
-    yh = gd.gcn_layer_sharded(sh, x[loh:hih].contiguous(), w, norm[loh:hih].contiguous(),
+    own = sh.owned_rows                             # source rows are dealt to the ranks by a hash of their id
+    yh = gd.gcn_layer_sharded(sh, x[own].contiguous(), w, norm[own].contiguous(),
                               norm[sh.shard.row0:sh.shard.row1].contiguous())
     fullh = sh.gather_outputs(yh)
     # GAT on the same graph: z, el, er gathered, fused attention on the local rows
