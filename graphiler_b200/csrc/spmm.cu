@@ -59,24 +59,120 @@ __device__ __forceinline__ void unpack_pairs<__nv_bfloat16>(const uint4 &r, uint
   for (int i = 0; i < 4; ++i) v[i] = pack2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
 }
 
-// EXACT: compensated (two-sum) accumulation, the default contract of the library.  !EXACT: plain
-// fp32 adds (opt-in; the same arithmetic as the reference's kernels, a third of the instructions).
-// Both work on packed pairs of columns.
-template <bool EXACT>
+// Accumulator kinds, all on packed pairs of columns.  1: compensated (two-sum) fp32, the library's contract.
+// 0: plain fp32 adds (opt-in; the same arithmetic as the reference's kernels, a third of the instructions).
+// 2: one double per column (the sum of fp32 terms in double is exact to 2^-53 per addition, and products of two
+// fp32 values are exact in double): the same contract as 1 on the fp64 pipe.  `hi` / `lo` then hold the bit
+// patterns of the two doubles, so that zeroing, shuffling and merging read the same as for kind 1.
+template <int KIND>
 struct AccT;
 template <>
-struct AccT<true> : Acc2 {};
+struct AccT<1> : Acc2 {
+  using Acc2::add;
+  using Acc2::fma_exact;
+  using Acc2::merge;
+  using Acc2::value;
+  __device__ __forceinline__ void add(uint64_t v, int) { Acc2::add(v); }
+  __device__ __forceinline__ void fma_exact(uint64_t p, uint64_t q, int) { Acc2::fma_exact(p, q); }
+  __device__ __forceinline__ void merge(uint64_t ohi, uint64_t olo, int) { Acc2::merge(ohi, olo); }
+  __device__ __forceinline__ uint64_t value(int) const { return Acc2::value(); }
+  __device__ __forceinline__ void planes(float &h0, float &h1, float &l0, float &l1, int = 0) const {
+    unpack2(hi, h0, h1);
+    unpack2(lo, l0, l1);
+  }
+};
 template <>
-struct AccT<false> {
+struct AccT<0> {
   uint64_t hi;
   static constexpr uint64_t lo = 0;
-  __device__ __forceinline__ void add(uint64_t v) { hi = fadd2(hi, v); }
-  __device__ __forceinline__ void fma_exact(uint64_t a, uint64_t b) { hi = ffma2(a, b, hi); }
-  __device__ __forceinline__ void merge(uint64_t ohi, uint64_t) { hi = fadd2(hi, ohi); }
-  __device__ __forceinline__ uint64_t value() const { return hi; }
+  __device__ __forceinline__ void add(uint64_t v, int = 0) { hi = fadd2(hi, v); }
+  __device__ __forceinline__ void fma_exact(uint64_t a, uint64_t b, int = 0) { hi = ffma2(a, b, hi); }
+  __device__ __forceinline__ void merge(uint64_t ohi, uint64_t, int = 0) { hi = fadd2(hi, ohi); }
+  __device__ __forceinline__ uint64_t value(int = 0) const { return hi; }
+  __device__ __forceinline__ void planes(float &h0, float &h1, float &l0, float &l1, int = 0) const {
+    unpack2(hi, h0, h1);
+    l0 = l1 = 0.f;
+  }
+};
+template <>
+struct AccT<2> {
+  uint64_t hi, lo;                    // bits of the even and the odd column's double
+  static __device__ __forceinline__ double d(uint64_t b) { return __longlong_as_double((long long)b); }
+  static __device__ __forceinline__ uint64_t b(double v) { return (uint64_t)__double_as_longlong(v); }
+  __device__ __forceinline__ void add(uint64_t v, int = 0) {
+    float x, y;
+    unpack2(v, x, y);
+    hi = b(d(hi) + (double)x), lo = b(d(lo) + (double)y);
+  }
+  __device__ __forceinline__ void fma_exact(uint64_t p, uint64_t q, int = 0) {
+    float px, py, qx, qy;
+    unpack2(p, px, py);
+    unpack2(q, qx, qy);
+    hi = b(fma((double)px, (double)qx, d(hi))), lo = b(fma((double)py, (double)qy, d(lo)));
+  }
+  __device__ __forceinline__ void merge(uint64_t ohi, uint64_t olo, int = 0) {
+    hi = b(d(hi) + d(ohi)), lo = b(d(lo) + d(olo));
+  }
+  __device__ __forceinline__ uint64_t value(int = 0) const { return pack2((float)d(hi), (float)d(lo)); }
+  __device__ __forceinline__ void planes(float &h0, float &h1, float &l0, float &l1, int = 0) const {
+    h0 = (float)d(hi), h1 = (float)d(lo);
+    l0 = (float)(d(hi) - (double)h0), l1 = (float)(d(lo) - (double)h1);
+  }
 };
 
-template <typename T, int LPR, int NV, int MODE, bool EXACT>
+// 3: kind 2 for the even column pairs of a vector and kind 1 for the odd ones, so that the fp64 and the fp32 pipe
+// each carry half of the accumulation.  `k` is the pair's index inside its vector (a constant after unrolling).
+template <>
+struct AccT<3> {
+  uint64_t hi, lo;
+  __device__ __forceinline__ void add(uint64_t v, int k) {
+    if (k & 1) {
+      Acc2 t{hi, lo};
+      t.add(v);
+      hi = t.hi, lo = t.lo;
+    } else {
+      AccT<2> t{hi, lo};
+      t.add(v);
+      hi = t.hi, lo = t.lo;
+    }
+  }
+  __device__ __forceinline__ void fma_exact(uint64_t p, uint64_t q, int k) {
+    if (k & 1) {
+      Acc2 t{hi, lo};
+      t.fma_exact(p, q);
+      hi = t.hi, lo = t.lo;
+    } else {
+      AccT<2> t{hi, lo};
+      t.fma_exact(p, q);
+      hi = t.hi, lo = t.lo;
+    }
+  }
+  __device__ __forceinline__ void merge(uint64_t ohi, uint64_t olo, int k) {
+    if (k & 1) {
+      Acc2 t{hi, lo};
+      t.merge(ohi, olo);
+      hi = t.hi, lo = t.lo;
+    } else {
+      AccT<2> t{hi, lo};
+      t.merge(ohi, olo);
+      hi = t.hi, lo = t.lo;
+    }
+  }
+  __device__ __forceinline__ uint64_t value(int k) const {
+    if (k & 1) return Acc2{hi, lo}.value();
+    return AccT<2>{hi, lo}.value();
+  }
+  __device__ __forceinline__ void planes(float &h0, float &h1, float &l0, float &l1, int k) const {
+    if (k & 1) {
+      unpack2(hi, h0, h1);
+      unpack2(lo, l0, l1);
+    } else {
+      AccT<2>{hi, lo}.planes(h0, h1, l0, l1);
+    }
+  }
+};
+
+template <typename T, int LPR, int NV, int MODE, int EXACT>
 __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   constexpr int VEC = VecOf<T>::N;
   constexpr int G = 32 / LPR;              // neighbour rows streamed concurrently by one warp
@@ -199,7 +295,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
           unpack_pairs<T>(raw[u][v], val);
           if (MODE == COPY) {
 #pragma unroll
-            for (int k = 0; k < VP; ++k) acc[v][k].add(val[k]);
+            for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], k);
           } else {
             const float wgt = (e[u] < n) ? wsm[e[u] * a.H + head[v]] : 0.f;
             const uint64_t w2 = pack2(wgt, wgt);
@@ -208,8 +304,8 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
               // attention weights are softmax probabilities: the rounded products sum to at most max|x| in
               // magnitude, so their rounding (<= eps/2 of that) is far below tolerance and only the sum is
               // compensated; arbitrary edge weights (u_mul_e_sum) keep the exact product
-              if (MODE == GAT) acc[v][k].add(fmul2(val[k], w2));
-              else acc[v][k].fma_exact(val[k], w2);
+              if (MODE == GAT) acc[v][k].add(fmul2(val[k], w2), k);
+              else acc[v][k].fma_exact(val[k], w2, k);
             }
           }
         }
@@ -228,12 +324,12 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
         const uint64_t olo = EXACT ? __shfl_xor_sync(FULL, (unsigned long long)acc[v][k].lo, off) : 0ull;
         // both partners add in the same order (lower group first) and so hold identical values
         if ((lane & off) == 0) {
-          acc[v][k].merge(ohi, olo);
+          acc[v][k].merge(ohi, olo, k);
         } else {
           AccT<EXACT> t;
           t.hi = ohi;
           if constexpr (EXACT) t.lo = olo;
-          t.merge(acc[v][k].hi, acc[v][k].lo);
+          t.merge(acc[v][k].hi, acc[v][k].lo, k);
           acc[v][k] = t;
         }
       }
@@ -248,7 +344,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
       if (!cok[v]) continue;
       float o[VEC];
 #pragma unroll
-      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(), o[2 * k], o[2 * k + 1]);
+      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(k), o[2 * k], o[2 * k + 1]);
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
@@ -265,8 +361,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
 #pragma unroll
       for (int k = 0; k < VP; ++k) {
         float h0, h1, l0, l1;
-        unpack2(acc[v][k].hi, h0, h1);
-        unpack2(acc[v][k].lo, l0, l1);
+        acc[v][k].planes(h0, h1, l0, l1, k);
         hi[cv[v] * VEC + 2 * k] = h0, hi[cv[v] * VEC + 2 * k + 1] = h1;
         lo[cv[v] * VEC + 2 * k] = l0, lo[cv[v] * VEC + 2 * k + 1] = l1;
       }
@@ -278,7 +373,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
 // Rows of at most 8 vectors (32 fp32 columns): a warp per item would leave most lanes idle on a low-degree row, so
 // LPR lanes take one item and a warp serves 32 / LPR items.  The lanes walk the item's positions in order, four rows in
 // flight, with no exchange between lanes.  The plan orders items by length, so the groups of a warp finish together.
-template <typename T, int LPR, int MODE, bool EXACT>
+template <typename T, int LPR, int MODE, int EXACT>
 __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int64_t first_item) {
   constexpr int VEC = VecOf<T>::N, VP = VEC / 2;
   const int l = threadIdx.x % LPR;
@@ -314,9 +409,9 @@ __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int6
     const uint64_t w2 = pack2(wgt, wgt);
 #pragma unroll
     for (int k = 0; k < VP; ++k) {
-      if (MODE == COPY) acc[k].add(val[k]);
-      else if (MODE == GAT) acc[k].add(fmul2(val[k], w2));
-      else acc[k].fma_exact(val[k], w2);
+      if (MODE == COPY) acc[k].add(val[k], k);
+      else if (MODE == GAT) acc[k].add(fmul2(val[k], w2), k);
+      else acc[k].fma_exact(val[k], w2, k);
     }
   };
   int i = it.begin;
@@ -344,7 +439,7 @@ __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int6
     const float scale = a.dst_scale ? __ldg(a.dst_scale + it.row) : 1.f;
     float o[VEC];
 #pragma unroll
-    for (int k = 0; k < VP; ++k) unpack2(acc[k].value(), o[2 * k], o[2 * k + 1]);
+    for (int k = 0; k < VP; ++k) unpack2(acc[k].value(k), o[2 * k], o[2 * k + 1]);
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
       if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
@@ -357,8 +452,7 @@ __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int6
 #pragma unroll
     for (int k = 0; k < VP; ++k) {
       float h0, h1, l0, l1;
-      unpack2(acc[k].hi, h0, h1);
-      unpack2(acc[k].lo, l0, l1);
+      acc[k].planes(h0, h1, l0, l1, k);
       hi[cv * VEC + 2 * k] = h0, hi[cv * VEC + 2 * k + 1] = h1;
       lo[cv * VEC + 2 * k] = l0, lo[cv * VEC + 2 * k + 1] = l1;
     }
@@ -393,7 +487,7 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
-template <typename T, int NV, bool EXACT>
+template <typename T, int NV, int EXACT>
 __global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(GatherArgs a, int stages_log2) {
   constexpr int VEC = VecOf<T>::N;
   constexpr int VP = VEC / 2;
@@ -465,7 +559,7 @@ __global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(Gather
       uint64_t val[VP];
       unpack_pairs<T>(raw[v], val);
 #pragma unroll
-      for (int k = 0; k < VP; ++k) acc[v][k].add(val[k]);
+      for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], k);
     }
     // every lane has consumed its part of the slot (the adds above depend on the loads): refill it
     const int jn = j + stages;
@@ -486,7 +580,7 @@ __global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(Gather
       if (!cok[v]) continue;
       float o[VEC];
 #pragma unroll
-      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(), o[2 * k], o[2 * k + 1]);
+      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(k), o[2 * k], o[2 * k + 1]);
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
@@ -503,8 +597,7 @@ __global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(Gather
 #pragma unroll
       for (int k = 0; k < VP; ++k) {
         float h0, h1, l0, l1;
-        unpack2(acc[v][k].hi, h0, h1);
-        unpack2(acc[v][k].lo, l0, l1);
+        acc[v][k].planes(h0, h1, l0, l1, k);
         const int c = (v * 32 + lane) * VEC + 2 * k;
         hi[c] = h0, hi[c + 1] = h1, lo[c] = l0, lo[c + 1] = l1;
       }
@@ -512,7 +605,7 @@ __global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(Gather
   }
 }
 
-template <typename T, int NV, bool EXACT>
+template <typename T, int NV, int EXACT>
 static int launch_bulk_e(const GatherArgs &a, cudaStream_t stream) {
   const uint32_t slot_bytes = ((uint32_t)a.FV * 16u + 127u) & ~127u;
   int stages_log2 = 4;                                                  // up to 16 rows in flight per warp,
@@ -596,7 +689,7 @@ __global__ void split_reduce_kernel(const int32_t *split_rows, const int32_t *sp
   from_f32(y[(int64_t)split_rows[r] * F + f], o);
 }
 
-template <typename T, int MODE, int LPR, int NV, bool EXACT>
+template <typename T, int MODE, int LPR, int NV, int EXACT>
 static int launch_vec_e(const GatherArgs &a, cudaStream_t stream) {
   const int tiles = (a.FV + LPR * NV - 1) / (LPR * NV);
   dim3 grid((unsigned)((a.n_items + WARPS - 1) / WARPS), (unsigned)tiles);
@@ -610,7 +703,7 @@ static int launch_vec_e(const GatherArgs &a, cudaStream_t stream) {
   return launched("gather_sum_kernel");
 }
 
-template <typename T, int MODE, int LPR, bool EXACT>
+template <typename T, int MODE, int LPR, int EXACT>
 static int launch_rows_e(const GatherArgs &a, int64_t first_item, cudaStream_t stream) {
   const int64_t threads = (a.n_items - first_item) * LPR;
   gather_sum_rows_kernel<T, LPR, MODE, EXACT><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(a, first_item);
@@ -635,8 +728,20 @@ static int launch_vec(const GatherArgs &a, cudaStream_t stream) {
                    : launch_rows_e<T, MODE, LPR, false>(a, a.n_long, stream);
     }
   }
-  if (!exact) return launch_vec_e<T, MODE, LPR, NV, false>(a, stream);
-  return launch_vec_e<T, MODE, LPR, NV, true>(a, stream);
+  if (!exact) return launch_vec_e<T, MODE, LPR, NV, 0>(a, stream);
+  // Which exact accumulator: measured on the 62 M-edge, 256-column gather, the unweighted sum is fastest with the
+  // columns split between the fp64 and the fp32 pipe (5.9 ms; two-sum alone 6.7, double alone 6.4), the edge-weighted
+  // sum with doubles alone (7.8 ms against 9.4: its exact product is one fused multiply-add in double and ten
+  // operations in fp32); the attention aggregate does not care (it waits on its per-edge weights).  GPHL_ACC =
+  // twosum | f64 | mixed overrides the choice.
+  static const int forced = [] {
+    const char *e = getenv("GPHL_ACC");
+    return !e ? 0 : std::string(e) == "twosum" ? 1 : std::string(e) == "f64" ? 2 : std::string(e) == "mixed" ? 3 : 0;
+  }();
+  const int kind = forced ? forced : (MODE == MUL_E ? 2 : 3);
+  if (kind == 1) return launch_vec_e<T, MODE, LPR, NV, 1>(a, stream);
+  if (kind == 2) return launch_vec_e<T, MODE, LPR, NV, 2>(a, stream);
+  return launch_vec_e<T, MODE, LPR, NV, 3>(a, stream);
 }
 
 template <typename T, int MODE>
