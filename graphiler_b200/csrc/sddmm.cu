@@ -3,7 +3,7 @@
 // One thread produces one 16-byte output vector (u_add_v) or one (edge, head) dot product
 // (u_dot_v); consecutive threads own consecutive outputs of the same edge, so the gathered
 // reads of one endpoint row and the output writes are contiguous.  Dot products are
-// accumulated with an exact-product compensated sum.
+// accumulated in double (exact products, 2^-53 per addition) and rounded once.
 #include <algorithm>
 
 #include "common.cuh"
@@ -34,16 +34,6 @@ __global__ void u_add_v_scalar_kernel(const I *__restrict__ src, const I *__rest
   }
 }
 
-// The two halves of a packed accumulator as one compensated value.
-__device__ __forceinline__ Acc join_halves(const Acc2 &p) {
-  float h0, h1, l0, l1;
-  unpack2(p.hi, h0, h1);
-  unpack2(p.lo, l0, l1);
-  Acc r{h0, l0};
-  r.merge(h1, l1);
-  return r;
-}
-
 template <typename I, bool VEC4>
 __global__ void u_dot_v_kernel(const I *__restrict__ src, const I *__restrict__ dst, int64_t n_edges, int32_t H,
                                int32_t D, const float *__restrict__ l, const float *__restrict__ r,
@@ -54,27 +44,26 @@ __global__ void u_dot_v_kernel(const I *__restrict__ src, const I *__restrict__ 
     const int h = (int)(t - e * H);
     const float *a = l + ((int64_t)__ldg(src + e) * H + h) * D;
     const float *b = r + ((int64_t)__ldg(dst + e) * H + h) * D;
+    // products of fp32 values are exact in double and each addition errs by 2^-53: the dot product is exact to the
+    // final rounding, with one fused multiply-add per term (the compensated fp32 form takes ten operations)
+    double acc = 0.0;
     if (VEC4) {
-      // even and odd elements in the two halves of a packed accumulator, joined at the end
-      Acc2 acc2{0, 0};
       for (int d = 0; d < D; d += 4) {
         const float4 p = __ldg(reinterpret_cast<const float4 *>(a + d));
         const float4 q = __ldg(reinterpret_cast<const float4 *>(b + d));
-        acc2.fma_exact(pack2(p.x, p.y), pack2(q.x, q.y));
-        acc2.fma_exact(pack2(p.z, p.w), pack2(q.z, q.w));
+        acc = fma((double)p.x, (double)q.x, acc), acc = fma((double)p.y, (double)q.y, acc);
+        acc = fma((double)p.z, (double)q.z, acc), acc = fma((double)p.w, (double)q.w, acc);
       }
-      z[t] = join_halves(acc2).value();
     } else {
-      Acc acc{0.f, 0.f};
-      for (int d = 0; d < D; ++d) acc.fma_exact(__ldg(a + d), __ldg(b + d));
-      z[t] = acc.value();
+      for (int d = 0; d < D; ++d) acc = fma((double)__ldg(a + d), (double)__ldg(b + d), acc);
     }
+    z[t] = (float)acc;
   }
 }
 
 // u_dot_v with coalesced row reads: a sub-warp group of LPR lanes reads one edge's two endpoint rows, NV consecutive
-// 16-byte vectors per lane (all of one head: NV divides the DV = D / 4 vectors of a head), multiplies exactly in
-// packed pairs, and the DV / NV lanes that share a head reduce with shuffles.  32 / LPR edges are in flight per
+// 16-byte vectors per lane (all of one head: NV divides the DV = D / 4 vectors of a head), multiplies and sums in
+// double (exact products), and the DV / NV lanes that share a head reduce with shuffles.  32 / LPR edges are in flight per
 // warp instruction, U per group.
 template <typename I, int LPR, int NV>
 __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__ src, const I *__restrict__ dst,
@@ -109,18 +98,15 @@ __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        Acc2 acc2{0, 0};
+        double acc0 = 0.0, acc1 = 0.0;                          // two chains: even and odd elements
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          acc2.fma_exact(pack2(a[u][v].x, a[u][v].y), pack2(b[u][v].x, b[u][v].y));
-          acc2.fma_exact(pack2(a[u][v].z, a[u][v].w), pack2(b[u][v].z, b[u][v].w));
+          acc0 = fma((double)a[u][v].x, (double)b[u][v].x, acc0), acc1 = fma((double)a[u][v].y, (double)b[u][v].y, acc1);
+          acc0 = fma((double)a[u][v].z, (double)b[u][v].z, acc0), acc1 = fma((double)a[u][v].w, (double)b[u][v].w, acc1);
         }
-        Acc acc = join_halves(acc2);
-        for (int off = 1; off < lanes_per_head; off <<= 1) {   // a power of two <= LPR
-          const float ohi = __shfl_xor_sync(FULL, acc.hi, off), olo = __shfl_xor_sync(FULL, acc.lo, off);
-          acc.merge(ohi, olo);
-        }
-        if (e[u] < n && cok && (ll % lanes_per_head) == 0) z[(base + e[u]) * H + cv0 / DV] = acc.value();
+        double acc = acc0 + acc1;
+        for (int off = 1; off < lanes_per_head; off <<= 1) acc += __shfl_xor_sync(FULL, acc, off);   // a power of two <= LPR
+        if (e[u] < n && cok && (ll % lanes_per_head) == 0) z[(base + e[u]) * H + cv0 / DV] = (float)acc;
       }
     }
   }
