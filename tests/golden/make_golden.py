@@ -1,7 +1,7 @@
 """Regenerate the golden fixtures of this directory.
 
-    python tests/golden/make_golden.py            (from the repository root; needs /root/reference for the one-off
-                                                   build of oracle/_ref by oracle/build_ref.py)
+    python tests/golden/make_golden.py            (from the repository root; needs the reference's source tree for the
+                                                   one-off build of oracle/_ref by oracle/build_ref.py)
 
 ref_flow_golden.npz / ref_flow_ops.json: seeded inputs, the outputs of the reference's own compiler flow
 (its MP-DFG builder and optimizer compiled from its sources, executing on the CPU operator registration

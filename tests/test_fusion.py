@@ -20,7 +20,7 @@ def run_cases(lib: Path, device: str):
     return json.loads(line[len("REPORT "):])
 
 
-def judge(rep, exact: bool):
+def assess(rep, exact: bool):
     assert len(rep) >= 10
     for name, c in rep.items():
         assert c["emitted"] == c["expected"], (name, c)
@@ -34,11 +34,11 @@ def test_fusion_patterns_cpu_registration():
     lib = REF / "libgraphiler_cpu.so"
     if not lib.exists():
         pytest.skip("oracle/_ref is not built (python oracle/build_ref.py needs the reference sources)")
-    judge(run_cases(lib, "cpu"), exact=True)
+    assess(run_cases(lib, "cpu"), exact=True)
 
 
 @pytest.mark.gpu
 def test_fusion_patterns_cuda_library():
     from graphiler_b200 import capi
     assert capi.TORCH_OPS_LIB.exists(), "libgraphiler.so is not built"
-    judge(run_cases(capi.TORCH_OPS_LIB, "cuda"), exact=False)
+    assess(run_cases(capi.TORCH_OPS_LIB, "cuda"), exact=False)

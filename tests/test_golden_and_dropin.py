@@ -83,7 +83,7 @@ OPS_AFTER_EXTRA_FUSION = {
 }
 
 
-def judge(rep):
+def assess(rep):
     want_ops = json.loads((GOLDEN / "ref_flow_ops.json").read_text())
     want_ops.update(OPS_AFTER_EXTRA_FUSION)
     for k, v in want_ops.items():
@@ -102,11 +102,11 @@ def judge(rep):
 
 
 def test_reference_compiler_dispatches_to_cpu_registration():
-    judge(run_ref_flow(REF / "libgraphiler_cpu.so", "cpu"))
+    assess(run_ref_flow(REF / "libgraphiler_cpu.so", "cpu"))
 
 
 @pytest.mark.gpu
 def test_reference_compiler_dispatches_to_cuda_library():
     from graphiler_b200 import capi
     assert capi.TORCH_OPS_LIB.exists(), "libgraphiler.so is not built"
-    judge(run_ref_flow(capi.TORCH_OPS_LIB, "cuda"))
+    assess(run_ref_flow(capi.TORCH_OPS_LIB, "cuda"))

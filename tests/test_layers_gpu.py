@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def judge(got, truth64, ref32):
+def assess(got, truth64, ref32):
     truth = truth64.numpy()
     _, bad_ref, _ = O.within_tolerance(ref32.numpy(), truth)
     _, bad_got, err = O.within_tolerance(got.float().cpu().numpy(), truth)
@@ -42,7 +42,7 @@ def test_gat_layer(fused):
     pg = layers.PreparedGraph(w.graph)
     out = layers.gat_layer(pg, w.feats, w.params["fc_weight"], w.params["attn_src"], w.params["attn_dst"], hy["slope"],
                            fused=fused)
-    judge(out, truth, ref32)
+    assess(out, truth, ref32)
 
 
 def test_gcn_two_layers():
@@ -58,7 +58,7 @@ def test_gcn_two_layers():
     n = layers.gcn_norms(pg)
     h = layers.gcn_layer(pg, w.feats, w.params["w1"], n, n)
     out = layers.gcn_layer(pg, h, w.params["w2"], n, n, relu=False)
-    judge(out, truth, ref32)
+    assess(out, truth, ref32)
 
 
 def test_rgcn_two_layers():
@@ -72,7 +72,7 @@ def test_rgcn_two_layers():
     pg = layers.PreparedGraph(w.graph)
     h = torch.relu(layers.rgcn_layer(pg, w.feats, w.params["w1"], w.edata["norm"]))
     out = layers.rgcn_layer(pg, h, w.params["w2"], w.edata["norm"])
-    judge(out, truth, ref32)
+    assess(out, truth, ref32)
 
 
 def test_hgt_layer():
@@ -84,4 +84,4 @@ def test_hgt_layer():
     w = wl.to(DEV)
     pg = layers.PreparedGraph(w.graph)
     out = layers.hgt_layer(pg, w.feats, w.params, hy["heads"], hy["sqrt_dk"])
-    judge(out, truth, ref32)
+    assess(out, truth, ref32)
