@@ -5,7 +5,7 @@
 // pointer, so the pointer is never copied to the host.  Row tiles never straddle a type
 // boundary.  Optional row gather (x[gather_idx[i]]) fuses the node->edge broadcast that
 // precedes the edge-typed linear.  This file holds the exact-fp32 SIMT path (shared-memory
-// tiled, 4x4 register blocking, exact-product compensated accumulation), the fallback for
+// tiled, 4x4 register blocking, products and sums in double), the fallback for
 // shapes the tensor-core kernel does not take, and the kernel for narrow weights (K <= 64,
 // N <= 32: a relation matrix of a few KB), where a 128-row tensor-core tile is mostly padding and
 // per-tile latency: one thread per (row, four output columns), the type's weights widened to
@@ -61,11 +61,12 @@ __global__ void __launch_bounds__(256) segment_mm_simt_kernel(const float *__res
   const int tx = tid & 15, ty = tid >> 4;
   const float *wt = w + (int64_t)seg * K * N;
 
-  Acc acc[4][4];   // compensated: a plain fp32 chain of a few hundred products misses atol 1e-6 now and then
+  double acc[4][4];   // a plain fp32 chain of a few hundred products misses atol 1e-6 now and then; products of fp32
+                      // values are exact in double and each addition errs by 2^-53
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j].hi = 0.f, acc[i][j].lo = 0.f;
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
 
   for (int k0 = 0; k0 < K; k0 += TK) {
 #pragma unroll
@@ -86,15 +87,15 @@ __global__ void __launch_bounds__(256) segment_mm_simt_kernel(const float *__res
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < TK; ++kk) {
-      float a[4], b[4];
+      double a[4], b[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+      for (int i = 0; i < 4; ++i) a[i] = (double)As[kk][ty * 4 + i];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+      for (int j = 0; j < 4; ++j) b[j] = (double)Bs[kk][tx * 4 + j];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j].fma_exact(a[i], b[j]);
+        for (int j = 0; j < 4; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
     }
     __syncthreads();
   }
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(256) segment_mm_simt_kernel(const float *__res
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int c = n0 + tx * 4 + j;
-      if (c < N) y[(int64_t)(row0 + r) * N + c] = acc[i][j].value();
+      if (c < N) y[(int64_t)(row0 + r) * N + c] = (float)acc[i][j];
     }
   }
 }
