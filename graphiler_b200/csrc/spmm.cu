@@ -120,58 +120,59 @@ struct AccT<2> {
   }
 };
 
-// 3: kind 2 for the even column pairs of a vector and kind 1 for the odd ones, so that the fp64 and the fp32 pipe
-// each carry half of the accumulation.  `k` is the pair's index inside its vector (a constant after unrolling).
+// 3: kind 2 for every second column pair of a lane and kind 1 for the others, so that the fp64 and the fp32 pipe
+// each carry half of the accumulation (measured against one pair in four and three in four: 6.0 ms against 6.5 and
+// 6.4 on the 62 M-edge, 256-column gather).  `k` numbers the pairs a lane holds (a constant after unrolling).
 template <>
 struct AccT<3> {
   uint64_t hi, lo;
+  static __device__ __forceinline__ bool in_double(int k) { return (k & 1) == 0; }
   __device__ __forceinline__ void add(uint64_t v, int k) {
-    if (k & 1) {
-      Acc2 t{hi, lo};
+    if (in_double(k)) {
+      AccT<2> t{hi, lo};
       t.add(v);
       hi = t.hi, lo = t.lo;
     } else {
-      AccT<2> t{hi, lo};
+      Acc2 t{hi, lo};
       t.add(v);
       hi = t.hi, lo = t.lo;
     }
   }
   __device__ __forceinline__ void fma_exact(uint64_t p, uint64_t q, int k) {
-    if (k & 1) {
-      Acc2 t{hi, lo};
+    if (in_double(k)) {
+      AccT<2> t{hi, lo};
       t.fma_exact(p, q);
       hi = t.hi, lo = t.lo;
     } else {
-      AccT<2> t{hi, lo};
+      Acc2 t{hi, lo};
       t.fma_exact(p, q);
       hi = t.hi, lo = t.lo;
     }
   }
   __device__ __forceinline__ void merge(uint64_t ohi, uint64_t olo, int k) {
-    if (k & 1) {
-      Acc2 t{hi, lo};
+    if (in_double(k)) {
+      AccT<2> t{hi, lo};
       t.merge(ohi, olo);
       hi = t.hi, lo = t.lo;
     } else {
-      AccT<2> t{hi, lo};
+      Acc2 t{hi, lo};
       t.merge(ohi, olo);
       hi = t.hi, lo = t.lo;
     }
   }
   __device__ __forceinline__ uint64_t value(int k) const {
-    if (k & 1) return Acc2{hi, lo}.value();
-    return AccT<2>{hi, lo}.value();
+    if (in_double(k)) return AccT<2>{hi, lo}.value();
+    return Acc2{hi, lo}.value();
   }
   __device__ __forceinline__ void planes(float &h0, float &h1, float &l0, float &l1, int k) const {
-    if (k & 1) {
+    if (in_double(k)) {
+      AccT<2>{hi, lo}.planes(h0, h1, l0, l1);
+    } else {
       unpack2(hi, h0, h1);
       unpack2(lo, l0, l1);
-    } else {
-      AccT<2>{hi, lo}.planes(h0, h1, l0, l1);
     }
   }
 };
-
 template <typename T, int LPR, int NV, int MODE, int EXACT>
 __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   constexpr int VEC = VecOf<T>::N;
@@ -295,7 +296,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
           unpack_pairs<T>(raw[u][v], val);
           if (MODE == COPY) {
 #pragma unroll
-            for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], k);
+            for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], v * VP + k);
           } else {
             const float wgt = (e[u] < n) ? wsm[e[u] * a.H + head[v]] : 0.f;
             const uint64_t w2 = pack2(wgt, wgt);
@@ -304,8 +305,8 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
               // attention weights are softmax probabilities: the rounded products sum to at most max|x| in
               // magnitude, so their rounding (<= eps/2 of that) is far below tolerance and only the sum is
               // compensated; arbitrary edge weights (u_mul_e_sum) keep the exact product
-              if (MODE == GAT) acc[v][k].add(fmul2(val[k], w2), k);
-              else acc[v][k].fma_exact(val[k], w2, k);
+              if (MODE == GAT) acc[v][k].add(fmul2(val[k], w2), v * VP + k);
+              else acc[v][k].fma_exact(val[k], w2, v * VP + k);
             }
           }
         }
@@ -324,12 +325,12 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
         const uint64_t olo = EXACT ? __shfl_xor_sync(FULL, (unsigned long long)acc[v][k].lo, off) : 0ull;
         // both partners add in the same order (lower group first) and so hold identical values
         if ((lane & off) == 0) {
-          acc[v][k].merge(ohi, olo, k);
+          acc[v][k].merge(ohi, olo, v * VP + k);
         } else {
           AccT<EXACT> t;
           t.hi = ohi;
           if constexpr (EXACT) t.lo = olo;
-          t.merge(acc[v][k].hi, acc[v][k].lo, k);
+          t.merge(acc[v][k].hi, acc[v][k].lo, v * VP + k);
           acc[v][k] = t;
         }
       }
@@ -344,7 +345,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
       if (!cok[v]) continue;
       float o[VEC];
 #pragma unroll
-      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(k), o[2 * k], o[2 * k + 1]);
+      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(v * VP + k), o[2 * k], o[2 * k + 1]);
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
@@ -361,7 +362,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
 #pragma unroll
       for (int k = 0; k < VP; ++k) {
         float h0, h1, l0, l1;
-        acc[v][k].planes(h0, h1, l0, l1, k);
+        acc[v][k].planes(h0, h1, l0, l1, v * VP + k);
         hi[cv[v] * VEC + 2 * k] = h0, hi[cv[v] * VEC + 2 * k + 1] = h1;
         lo[cv[v] * VEC + 2 * k] = l0, lo[cv[v] * VEC + 2 * k + 1] = l1;
       }
@@ -559,7 +560,7 @@ __global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(Gather
       uint64_t val[VP];
       unpack_pairs<T>(raw[v], val);
 #pragma unroll
-      for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], k);
+      for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], v * VP + k);
     }
     // every lane has consumed its part of the slot (the adds above depend on the loads): refill it
     const int jn = j + stages;
@@ -580,7 +581,7 @@ __global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(Gather
       if (!cok[v]) continue;
       float o[VEC];
 #pragma unroll
-      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(k), o[2 * k], o[2 * k + 1]);
+      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(v * VP + k), o[2 * k], o[2 * k + 1]);
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
@@ -597,7 +598,7 @@ __global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(Gather
 #pragma unroll
       for (int k = 0; k < VP; ++k) {
         float h0, h1, l0, l1;
-        acc[v][k].planes(h0, h1, l0, l1, k);
+        acc[v][k].planes(h0, h1, l0, l1, v * VP + k);
         const int c = (v * 32 + lane) * VEC + 2 * k;
         hi[c] = h0, hi[c + 1] = h1, lo[c] = l0, lo[c + 1] = l1;
       }
