@@ -47,13 +47,18 @@ __global__ void u_dot_v_kernel(const I *__restrict__ src, const I *__restrict__ 
     // products of fp32 values are exact in double and each addition errs by 2^-53: the dot product is exact to the
     // final rounding, with one fused multiply-add per term (the compensated fp32 form takes ten operations)
     double acc = 0.0;
+    Acc2 acc2{0, 0};
     if (VEC4) {
       for (int d = 0; d < D; d += 4) {
         const float4 p = __ldg(reinterpret_cast<const float4 *>(a + d));
         const float4 q = __ldg(reinterpret_cast<const float4 *>(b + d));
         acc = fma((double)p.x, (double)q.x, acc), acc = fma((double)p.y, (double)q.y, acc);
-        acc = fma((double)p.z, (double)q.z, acc), acc = fma((double)p.w, (double)q.w, acc);
+        acc2.fma_exact(pack2(p.z, p.w), pack2(q.z, q.w));           // the other half on the fp32 pipe
       }
+      float h0, h1, l0, l1;
+      unpack2(acc2.hi, h0, h1);
+      unpack2(acc2.lo, l0, l1);
+      acc += ((double)h0 + (double)h1) + ((double)l0 + (double)l1);
     } else {
       for (int d = 0; d < D; ++d) acc = fma((double)__ldg(a + d), (double)__ldg(b + d), acc);
     }
@@ -62,8 +67,8 @@ __global__ void u_dot_v_kernel(const I *__restrict__ src, const I *__restrict__ 
 }
 
 // u_dot_v with coalesced row reads: a sub-warp group of LPR lanes reads one edge's two endpoint rows, NV consecutive
-// 16-byte vectors per lane (all of one head: NV divides the DV = D / 4 vectors of a head), multiplies and sums in
-// double (exact products), and the DV / NV lanes that share a head reduce with shuffles.  32 / LPR edges are in flight per
+// 16-byte vectors per lane (all of one head: NV divides the DV = D / 4 vectors of a head), multiplies exactly (half
+// of the terms in double, half as compensated fp32 pairs), and the DV / NV lanes that share a head reduce with shuffles.  32 / LPR edges are in flight per
 // warp instruction, U per group.
 template <typename I, int LPR, int NV>
 __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__ src, const I *__restrict__ dst,
@@ -98,13 +103,20 @@ __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        double acc0 = 0.0, acc1 = 0.0;                          // two chains: even and odd elements
+        // Exact products on both pipes (the fp64 pipe alone bounds this kernel, as the fp32 pipe alone did): the first
+        // half of every vector in double (a product of fp32 values is exact there), the second as packed fp32
+        // products with their rounding errors in a compensated pair; joined in double.
+        double accd = 0.0;
+        Acc2 acc2{0, 0};
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          acc0 = fma((double)a[u][v].x, (double)b[u][v].x, acc0), acc1 = fma((double)a[u][v].y, (double)b[u][v].y, acc1);
-          acc0 = fma((double)a[u][v].z, (double)b[u][v].z, acc0), acc1 = fma((double)a[u][v].w, (double)b[u][v].w, acc1);
+          accd = fma((double)a[u][v].x, (double)b[u][v].x, accd), accd = fma((double)a[u][v].y, (double)b[u][v].y, accd);
+          acc2.fma_exact(pack2(a[u][v].z, a[u][v].w), pack2(b[u][v].z, b[u][v].w));
         }
-        double acc = acc0 + acc1;
+        float h0, h1, l0, l1;
+        unpack2(acc2.hi, h0, h1);
+        unpack2(acc2.lo, l0, l1);
+        double acc = accd + (((double)h0 + (double)h1) + ((double)l0 + (double)l1));
         for (int off = 1; off < lanes_per_head; off <<= 1) acc += __shfl_xor_sync(FULL, acc, off);   // a power of two <= LPR
         if (e[u] < n && cok && (ll % lanes_per_head) == 0) z[(base + e[u]) * H + cv0 / DV] = (float)acc;
       }
