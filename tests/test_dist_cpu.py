@@ -84,9 +84,9 @@ def _worker(rank, world, port, tmp):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2])
-def test_sharded_gcn_layer_two_gloo_ranks(world, tmp_path):
-    port = 29500 + os.getpid() % 2000
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_gcn_layer_gloo_ranks(world, tmp_path):
+    port = 29500 + os.getpid() % 2000 + world
     mp.start_processes(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True, start_method="spawn")
     ok = np.load(tmp_path / "ok.npy")
     assert ok.all(), ok

@@ -336,6 +336,19 @@ def test_ops_on_config_shaped_graphs(name, scale):
     close(a, O.segment_softmax(w.cpu() * 5, graph.in_pointer, graph.in_edge_indices))
 
 
+@pytest.mark.parametrize("kind", ["twosum", "f64", "mixed"])
+def test_gather_accumulator_kinds(kind):
+    """The three exact accumulators of the gather kernels (compensated fp32, double, half of the column pairs each)
+    meet the same tolerance; the library picks one per operator, GPHL_ACC forces one for the whole process."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, GPHL_ACC=kind)
+    r = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "acc_kinds_case.py")], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and r.stdout.strip().endswith("OK"), r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_bounded_wait_gives_up_and_reports():
     """Failure detection without a fault: a wait on a barrier that nothing completes runs out after its poll limit,
     is counted, and the context stays usable."""
