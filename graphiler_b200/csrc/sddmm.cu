@@ -220,8 +220,8 @@ extern "C" int gphl_sddmm_u_dot_v_f32_i32(const int32_t *src, const int32_t *dst
 
 // ---- attention scores per node and head: el[n,h] = sum_d z[n,h,d] a_src[h,d], er likewise with a_dst ----
 // The dense prologue of the GAT layer (the reference computes it as mm(z, attn_weight) after its split pass,
-// examples/GAT/GAT.py:25-31).  One sub-warp group of `lanes` threads per node row reads the row once with 16-byte
-// loads and produces both score vectors; products are accumulated exactly (compensated) and reduced with shuffles.
+// examples/GAT/GAT.py:25-31).  One thread per (node, head) reads the head's slice of the row once with 16-byte loads
+// and produces both scores from exact products.
 namespace gphl {
 
 __global__ void head_scores_kernel(const float *__restrict__ z, const float *__restrict__ a_src,
@@ -233,24 +233,35 @@ __global__ void head_scores_kernel(const float *__restrict__ z, const float *__r
   const int h = (int)(t % H);
   const float *row = z + t * D;                      // (n*H + h) * D
   const float *as = a_src + (int64_t)h * D, *ad = a_dst + (int64_t)h * D;
-  Acc s{0.f, 0.f}, d{0.f, 0.f};
-  if ((D & 3) == 0 && aligned16_dev(row)) {
+  // both dot products exact to the last rounding, one on each floating-point pipe: el in double (exact products),
+  // er as packed fp32 products with their rounding errors in a compensated pair
+  double s = 0.0;
+  if ((D & 3) == 0 && aligned16_dev(row) && aligned16_dev(as) && aligned16_dev(ad)) {
+    Acc2 d2{0, 0};
     for (int k = 0; k < D; k += 4) {
       const float4 v = __ldg(reinterpret_cast<const float4 *>(row + k));
-      s.fma_exact(v.x, __ldg(as + k)), s.fma_exact(v.y, __ldg(as + k + 1));
-      s.fma_exact(v.z, __ldg(as + k + 2)), s.fma_exact(v.w, __ldg(as + k + 3));
-      d.fma_exact(v.x, __ldg(ad + k)), d.fma_exact(v.y, __ldg(ad + k + 1));
-      d.fma_exact(v.z, __ldg(ad + k + 2)), d.fma_exact(v.w, __ldg(ad + k + 3));
+      const float4 p = __ldg(reinterpret_cast<const float4 *>(as + k));
+      const float4 q = __ldg(reinterpret_cast<const float4 *>(ad + k));
+      s = fma((double)v.x, (double)p.x, s), s = fma((double)v.y, (double)p.y, s);
+      s = fma((double)v.z, (double)p.z, s), s = fma((double)v.w, (double)p.w, s);
+      d2.fma_exact(pack2(v.x, v.y), pack2(q.x, q.y));
+      d2.fma_exact(pack2(v.z, v.w), pack2(q.z, q.w));
     }
+    float h0, h1, l0, l1;
+    unpack2(d2.hi, h0, h1);
+    unpack2(d2.lo, l0, l1);
+    el[t] = (float)s;
+    er[t] = (float)(((double)h0 + (double)h1) + ((double)l0 + (double)l1));
   } else {
+    double d = 0.0;
     for (int k = 0; k < D; ++k) {
-      const float v = __ldg(row + k);
-      s.fma_exact(v, __ldg(as + k));
-      d.fma_exact(v, __ldg(ad + k));
+      const double v = (double)__ldg(row + k);
+      s = fma(v, (double)__ldg(as + k), s);
+      d = fma(v, (double)__ldg(ad + k), d);
     }
+    el[t] = (float)s;
+    er[t] = (float)d;
   }
-  el[t] = s.value();
-  er[t] = d.value();
 }
 
 }  // namespace gphl
