@@ -264,6 +264,79 @@ __global__ void head_scores_kernel(const float *__restrict__ z, const float *__r
   }
 }
 
+// The same scores with coalesced row reads, for rows of up to 128 vectors whose heads are a power-of-two number of
+// vectors: a group of LPR lanes reads a node's row as consecutive 16-byte vectors (NV per lane, all of one head), keeps
+// its columns of the two attention vectors in registers, and the lanes of a head reduce with shuffles.  The thread-per-
+// head kernel above reads 128-byte slices at a 128-byte stride between lanes and reaches a quarter of the bandwidth.
+template <int LPR, int NV>
+__global__ void __launch_bounds__(256) head_scores_rows_kernel(const float4 *__restrict__ z, const float4 *__restrict__ a_src,
+                                                               const float4 *__restrict__ a_dst, int64_t n, int32_t H,
+                                                               int32_t FV, int32_t DV, float *__restrict__ el,
+                                                               float *__restrict__ er) {
+  constexpr int G = 32 / LPR, U = (NV >= 2) ? 2 : 4;
+  const int lane = threadIdx.x & 31, g = lane / LPR, ll = lane % LPR;
+  const int cv0 = ll * NV;
+  const bool cok = cv0 < FV;
+  const int lanes_per_head = DV / NV;
+  double ps[NV][4];                                      // this lane's columns of a_src, widened once
+  float4 pd[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const float4 p = cok ? __ldg(a_src + cv0 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ps[v][0] = (double)p.x, ps[v][1] = (double)p.y, ps[v][2] = (double)p.z, ps[v][3] = (double)p.w;
+    pd[v] = cok ? __ldg(a_dst + cv0 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t base = warp_id * (G * U); base < n; base += n_warps * (G * U)) {
+    float4 a[U][NV];
+    int64_t r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      r[u] = base + u * G + g;
+      const bool ok = r[u] < n && cok;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) a[u][v] = ok ? __ldg(z + r[u] * FV + cv0 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      double s = 0.0;                                    // el: exact products in double
+      Acc2 d2{0, 0};                                     // er: packed fp32 products with their rounding errors
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        s = fma((double)a[u][v].x, ps[v][0], s), s = fma((double)a[u][v].y, ps[v][1], s);
+        s = fma((double)a[u][v].z, ps[v][2], s), s = fma((double)a[u][v].w, ps[v][3], s);
+        d2.fma_exact(pack2(a[u][v].x, a[u][v].y), pack2(pd[v].x, pd[v].y));
+        d2.fma_exact(pack2(a[u][v].z, a[u][v].w), pack2(pd[v].z, pd[v].w));
+      }
+      float h0, h1, l0, l1;
+      unpack2(d2.hi, h0, h1);
+      unpack2(d2.lo, l0, l1);
+      double d = ((double)h0 + (double)h1) + ((double)l0 + (double)l1);
+      for (int off = 1; off < lanes_per_head; off <<= 1) {     // a power of two <= LPR
+        s += __shfl_xor_sync(FULL, s, off);
+        d += __shfl_xor_sync(FULL, d, off);
+      }
+      if (r[u] < n && cok && (ll % lanes_per_head) == 0) {
+        el[r[u] * H + cv0 / DV] = (float)s;
+        er[r[u] * H + cv0 / DV] = (float)d;
+      }
+    }
+  }
+}
+
+template <int LPR, int NV>
+static int launch_head_scores_rows(const float *z, const float *a_src, const float *a_dst, int64_t n, int64_t heads,
+                                   int64_t fv, int64_t dv, float *el, float *er, cudaStream_t stream) {
+  constexpr int per_warp = (32 / LPR) * ((NV >= 2) ? 2 : 4);
+  const int64_t warps = (n + per_warp - 1) / per_warp;
+  const int64_t blocks = std::min<int64_t>((warps + 7) / 8, 148LL * 32);
+  head_scores_rows_kernel<LPR, NV><<<(unsigned)blocks, 256, 0, stream>>>(
+      reinterpret_cast<const float4 *>(z), reinterpret_cast<const float4 *>(a_src), reinterpret_cast<const float4 *>(a_dst),
+      n, (int32_t)heads, (int32_t)fv, (int32_t)dv, el, er);
+  return launched("head_scores_rows_kernel");
+}
+
 }  // namespace gphl
 
 extern "C" int gphl_gat_head_scores_f32(const float *z, const float *attn_src, const float *attn_dst, int64_t n_nodes,
@@ -271,6 +344,23 @@ extern "C" int gphl_gat_head_scores_f32(const float *z, const float *attn_src, c
   GPHL_REQUIRE(n_nodes >= 0 && heads >= 1 && dim >= 1 && heads * dim < (1 << 20), "bad sizes");
   if (n_nodes == 0) return GPHL_OK;
   GPHL_REQUIRE(z && attn_src && attn_dst && el && er, "null pointer argument");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int64_t dv = dim / 4, fv = heads * dim / 4;
+  if (dim % 4 == 0 && (dv & (dv - 1)) == 0 && dv <= 32 && fv <= 128 && gphl::aligned16(z) && gphl::aligned16(attn_src) &&
+      gphl::aligned16(attn_dst)) {
+    const int64_t nv = fv <= 32 ? 1 : fv <= 64 ? 2 : 4;       // vectors per lane; a lane must stay inside one head
+    if (dv % nv == 0) {
+      using namespace gphl;
+      if (nv == 4) return launch_head_scores_rows<32, 4>(z, attn_src, attn_dst, n_nodes, heads, fv, dv, el, er, stream);
+      if (nv == 2) return launch_head_scores_rows<32, 2>(z, attn_src, attn_dst, n_nodes, heads, fv, dv, el, er, stream);
+      if (fv <= 1) return launch_head_scores_rows<1, 1>(z, attn_src, attn_dst, n_nodes, heads, fv, dv, el, er, stream);
+      if (fv <= 2) return launch_head_scores_rows<2, 1>(z, attn_src, attn_dst, n_nodes, heads, fv, dv, el, er, stream);
+      if (fv <= 4) return launch_head_scores_rows<4, 1>(z, attn_src, attn_dst, n_nodes, heads, fv, dv, el, er, stream);
+      if (fv <= 8) return launch_head_scores_rows<8, 1>(z, attn_src, attn_dst, n_nodes, heads, fv, dv, el, er, stream);
+      if (fv <= 16) return launch_head_scores_rows<16, 1>(z, attn_src, attn_dst, n_nodes, heads, fv, dv, el, er, stream);
+      return launch_head_scores_rows<32, 1>(z, attn_src, attn_dst, n_nodes, heads, fv, dv, el, er, stream);
+    }
+  }
   const int64_t total = n_nodes * heads;
   gphl::head_scores_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       z, attn_src, attn_dst, n_nodes, (int32_t)heads, (int32_t)dim, el, er);

@@ -231,9 +231,9 @@ def test_gat_fused(graph, heads, dim, use_plan):
     close(out2, truth)
 
 
-@pytest.mark.parametrize("heads,dim", [(8, 8), (8, 32), (1, 64), (3, 5)])
+@pytest.mark.parametrize("heads,dim", [(8, 8), (8, 32), (1, 64), (3, 5), (4, 128), (16, 4), (2, 16), (1, 4), (8, 64), (2, 256)])
 def test_gat_head_scores(heads, dim):
-    z = torch.randn(1000, heads * dim, device=DEV)
+    z = torch.randn(1003, heads * dim, device=DEV)
     a_s, a_d = torch.randn(heads, dim, device=DEV), torch.randn(heads, dim, device=DEV)
     el, er = capi.gat_head_scores(z, a_s, a_d)
     zv = z.double().cpu().view(-1, heads, dim)
