@@ -3,7 +3,8 @@
   lib/libgphl.so        CUDA kernels + C ABI (include/gphl.h); no torch dependency
   lib/libgraphiler.so   TorchScript registrations (my_classes.DGLGraph, my_ops::*) over the C ABI
 
-``python -m graphiler_b200.build`` rebuilds whatever is out of date.  nvcc cross-compiles
+``python -m graphiler_b200.build [--force] [--measure]`` rebuilds whatever is out of date (``--measure`` adds
+lib/libgphl_measure.so, the same kernels with their tuning knobs readable from the environment).  nvcc cross-compiles
 without a GPU.  The reference builds its operator library for sm_70 with CMake
 (CMakeLists.txt:12-32); nothing of that build is reused.
 """
@@ -53,20 +54,24 @@ def kernel_sources():
     return [CSRC / s for s in KERNEL_SOURCES if (CSRC / s).exists()]
 
 
-def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile every .cu file to an object (in parallel) and link lib/libgphl.so."""
+def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool = False, measure: bool = False) -> Path:
+    """Compile every .cu file to an object (in parallel) and link lib/libgphl.so.
+
+    ``measure=True`` builds lib/libgphl_measure.so instead: the same sources with -DGPHL_MEASURE, in which the
+    tuning knobs of csrc/common.cuh are read from the environment.  Only the per-kernel timer loads it."""
     LIB.mkdir(exist_ok=True)
-    out = LIB / "libgphl.so"
+    out = LIB / ("libgphl_measure.so" if measure else "libgphl.so")
     srcs = kernel_sources()
     deps = srcs + list(CSRC.glob("*.cuh")) + [ROOT / "include" / "gphl.h"]
     if not force and not _stale(out, deps):
         return out
-    objdir = LIB / "obj"
+    objdir = LIB / ("obj_measure" if measure else "obj")
     objdir.mkdir(exist_ok=True)
     procs = []
     for s in srcs:
         o = objdir / (s.stem + ".o")
-        cmd = [_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if ptxas_info else []), "-c", s, "-o", o]
+        cmd = [_nvcc(), *NVCC_FLAGS, *(["-DGPHL_MEASURE"] if measure else []),
+               *(["-Xptxas", "-v"] if ptxas_info else []), "-c", s, "-o", o]
         if verbose:
             print(" ".join(str(c) for c in cmd), flush=True)
         procs.append((s, o, subprocess.Popen([str(c) for c in cmd], stdout=subprocess.PIPE,
@@ -116,4 +121,6 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
 
 if __name__ == "__main__":
     build_all(force="--force" in sys.argv, verbose=True)
+    if "--measure" in sys.argv:
+        build_kernels(force="--force" in sys.argv, verbose=True, measure=True)
     print("built:", *(p.name for p in LIB.glob("*.so")))

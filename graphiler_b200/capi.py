@@ -65,8 +65,10 @@ class GphlError(RuntimeError):
     pass
 
 
-def load_library(path: Optional[Path] = None):
-    """dlopen libgphl.so and set the prototypes.  Raises if it has not been built."""
+def load_library(path: Optional[Path] = None, make_default: bool = False):
+    """dlopen libgphl.so and set the prototypes.  Raises if it has not been built.  ``make_default`` makes the
+    library at ``path`` the one every wrapper of this module calls (the per-kernel timer uses it to load the
+    measurement build)."""
     global _lib
     if _lib is not None and path is None:
         return _lib
@@ -79,7 +81,7 @@ def load_library(path: Optional[Path] = None):
             raise GphlError(f"{p} does not export {name}: rebuild with `python -m graphiler_b200.build --force`")
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args
-    if path is None:
+    if path is None or make_default:
         _lib = lib
     return lib
 

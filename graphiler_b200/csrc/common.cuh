@@ -49,6 +49,15 @@ inline int launched(const char *what) {
     if (!(cond)) return ::gphl::fail(GPHL_ERR_INVALID_ARGUMENT, __VA_ARGS__);             \
   } while (0)
 
+// Integer tuning knobs.  The product library compiles every knob to its default; the measurement build
+// (-DGPHL_MEASURE, lib/libgphl_measure.so, used only by the per-kernel timer) reads them from the environment at
+// every call, so that variants of one kernel can be timed side by side in one process.
+#ifdef GPHL_MEASURE
+int knob(const char *name, int dflt);
+#else
+inline int knob(const char *, int dflt) { return dflt; }
+#endif
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- work items ------------------------------------------------------------------------

@@ -1,4 +1,5 @@
 // Host side of the library: error state, launch counter and the row-split plan.
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -18,6 +19,13 @@ void set_error(const char *fmt, ...) {
   va_end(ap);
   t_error = buf;
 }
+
+#ifdef GPHL_MEASURE
+int knob(const char *name, int dflt) {
+  const char *e = getenv(name);
+  return e ? atoi(e) : dflt;
+}
+#endif
 
 }  // namespace gphl
 
@@ -67,8 +75,7 @@ extern "C" int gphl_plan_create(const int32_t *pointer, int64_t n_rows, int32_t 
     for (const Item &it : items) start[(size_t)(chunk - (it.end - it.begin)) + 1]++;
     for (size_t i = 1; i < start.size(); ++i) start[i] += start[i - 1];
     // buckets are ordered by falling length: the long items are those in front of the first short bucket
-    int32_t short_item = GPHL_SHORT_ITEM;
-    if (const char *env = getenv("GPHL_SHORT_ITEM")) short_item = std::max(0, atoi(env));   // tuning knob
+    const int32_t short_item = std::max(0, knob("GPHL_SHORT_ITEM", GPHL_SHORT_ITEM));
     n_long = chunk > short_item ? start[(size_t)(chunk - short_item)] : 0;
     std::vector<Item> sorted(items.size());
     for (const Item &it : items) sorted[(size_t)start[(size_t)(chunk - (it.end - it.begin))]++] = it;

@@ -9,9 +9,6 @@
 // before accumulating, which keeps >= U KB per warp in flight.  Sums are compensated
 // (two-sum) fp32 in a fixed order; pieces of a cut row are combined in ascending order by a
 // second small kernel, so the result does not depend on the split or on the GPU count.
-#include <cstdlib>
-#include <string>
-
 #include "common.cuh"
 
 namespace gphl {
@@ -460,171 +457,127 @@ __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int6
   }
 }
 
-// ---- bulk-async (TMA) staged variant of the unweighted sum --------------------------------------
-// For rows of >= 512 B.  Each warp owns a ring of BULK_STAGES shared-memory slots, one source row per
-// slot, each guarded by an mbarrier.  An elected lane keeps the ring full with cp.async.bulk copies
-// (the copy engine moves a whole row per instruction and signals the slot's barrier with the byte
-// count), so the rows in flight cost no registers and the accumulation of row j overlaps the
-// fetch of rows j+1 .. j+BULK_STAGES.  No multicast: every copy reads this GPU's memory into this
-// block's shared memory.  Waits are bounded; a wait that runs out sets g_bulk_wait_timeouts, and the
-// warp drains what it issued (bounded again) and leaves its rows unwritten.
-constexpr int BULK_WARPS = 4;
-constexpr uint32_t BULK_WAIT_LIMIT = 1u << 22;
-__device__ int g_bulk_wait_timeouts = 0;
-
-__device__ __forceinline__ uint32_t s_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < BULK_WAIT_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-template <typename T, int NV, int EXACT>
-__global__ void __launch_bounds__(BULK_WARPS * 32) gather_sum_bulk_kernel(GatherArgs a, int stages_log2) {
-  constexpr int VEC = VecOf<T>::N;
-  constexpr int VP = VEC / 2;
-  extern __shared__ __align__(128) uint8_t bulk_smem[];
+// ---- column-sliced unweighted sum for matrices far larger than the L2 cache ----------------------------
+// A feature matrix of gigabytes gathered ~26 times per row is served from the 126 MB L2 only for its most popular
+// rows; everything else comes from DRAM once per edge.  Cutting the columns into slices of LPR 16-byte vectors and
+// running the slices one after the other (blockIdx.y, the slow grid dimension) shrinks the bytes a source row
+// occupies in the cache by the number of slices, so the cache holds that many more distinct sources, at the cost of
+// one more pass over the index array per slice.  A warp takes one work item and one slice: its 32 / LPR lane groups
+// walk the item's positions round-robin (group g takes positions g, g + G, ...), each lane holding one 16-byte
+// vector of the slice, U rows in flight per group, the next U indices fetched while the current rows are summed.
+// The groups' partial sums are merged in a fixed order, so the result depends only on the item and on LPR.
+template <typename T, int LPR, int EXACT>
+__global__ void __launch_bounds__(WARPS * 32) gather_sum_sliced_kernel(GatherArgs a) {
+  constexpr int VEC = VecOf<T>::N, VP = VEC / 2, G = 32 / LPR, U = 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int stages = 1 << stages_log2, smask = stages - 1;   // power of two: slot = j & smask, phase = (j >> log2) & 1
-  const int64_t item_id = (int64_t)blockIdx.x * BULK_WARPS + warp;
+  const int64_t item_id = (int64_t)blockIdx.x * WARPS + warp;
   if (item_id >= a.n_items) return;
   const Item it = fetch_item(a.items, a.pointer, item_id);
+  const int g = lane / LPR, l = lane % LPR;
+  int cv = blockIdx.y * LPR + l;
+  const bool cok = cv < a.FV;
+  if (!cok) cv = 0;
+
+  AccT<EXACT> acc[VP];
+#pragma unroll
+  for (int k = 0; k < VP; ++k) {
+    acc[k].hi = 0;
+    if constexpr (EXACT) acc[k].lo = 0;
+  }
+  const char *xb = static_cast<const char *>(a.x) + (size_t)cv * 16;
   const uint32_t row_bytes = (uint32_t)a.FV * 16u;
-  const uint32_t slot_bytes = (row_bytes + 127u) & ~127u;
-  uint8_t *ring = bulk_smem + (size_t)warp * stages * slot_bytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(bulk_smem + (size_t)BULK_WARPS * stages * slot_bytes) + warp * stages;
-  const uint32_t ring_s = s_addr(ring), bars_s = s_addr(bars);
-  if (lane == 0) {
-    for (int s = 0; s < stages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars_s + 8 * s));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  const int32_t *ip = a.idx + it.begin + g;
+  const int cnt = (it.end - it.begin - g + G - 1) / G;      // positions of this lane group
+  auto add_row = [&](const uint4 &raw) {
+    uint64_t val[VP];
+    unpack_pairs<T>(raw, val);
+#pragma unroll
+    for (int k = 0; k < VP; ++k) acc[k].add(val[k], k);
+  };
+  int i = 0;
+  int s[U];
+  if (U <= cnt) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) s[u] = __ldg(ip + u * G);
+  }
+#pragma unroll 1
+  for (; i + U <= cnt; i += U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) raw[u] = __ldg(reinterpret_cast<const uint4 *>(xb + (uint64_t)(uint32_t)s[u] * row_bytes));
+    if (i + 2 * U <= cnt) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) s[u] = __ldg(ip + (i + U + u) * G);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) add_row(raw[u]);
+  }
+  for (; i < cnt; ++i) {
+    const uint32_t src = (uint32_t)__ldg(ip + i * G);
+    add_row(__ldg(reinterpret_cast<const uint4 *>(xb + (uint64_t)src * row_bytes)));
   }
   __syncwarp();
 
-  bool cok[NV];
+  // combine the G lane groups in a fixed order (both partners add lower group first and hold identical values)
 #pragma unroll
-  for (int v = 0; v < NV; ++v) cok[v] = v * 32 + lane < a.FV;
-  AccT<EXACT> acc[NV][VP];
-#pragma unroll
-  for (int v = 0; v < NV; ++v)
+  for (int off = LPR; off < 32; off <<= 1) {
 #pragma unroll
     for (int k = 0; k < VP; ++k) {
-      acc[v][k].hi = 0;
-      if constexpr (EXACT) acc[v][k].lo = 0;
+      const uint64_t ohi = __shfl_xor_sync(FULL, (unsigned long long)acc[k].hi, off);
+      const uint64_t olo = EXACT ? __shfl_xor_sync(FULL, (unsigned long long)acc[k].lo, off) : 0ull;
+      if ((lane & off) == 0) {
+        acc[k].merge(ohi, olo, k);
+      } else {
+        AccT<EXACT> t;
+        t.hi = ohi;
+        if constexpr (EXACT) t.lo = olo;
+        t.merge(acc[k].hi, acc[k].lo, k);
+        acc[k] = t;
+      }
     }
-
-  const uint8_t *x = static_cast<const uint8_t *>(a.x);
-  const int cnt = it.end - it.begin;
-  auto issue = [&](int j, int src) {       // lane 0: fetch source row `src` into the slot of edge j
-    const uint32_t bar = bars_s + 8 * (j & smask), dst = ring_s + (j & smask) * slot_bytes;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(x + (int64_t)src * row_bytes), "r"(row_bytes), "r"(bar)
-                 : "memory");
-  };
-  // indices: lanes hold the batch of 32 that contains edge j and the batch after it
-  int cur_idx = 0, nxt_idx = 0;
-  if (lane < cnt) cur_idx = __ldcs(a.idx + it.begin + lane);
-  if (32 + lane < cnt) nxt_idx = __ldcs(a.idx + it.begin + 32 + lane);
-  // prologue: fill the ring (stages <= 32, so these edges are in the first batch or the second)
-  for (int j = 0; j < min(stages, cnt); ++j) {
-    const int src = __shfl_sync(FULL, j < 32 ? cur_idx : nxt_idx, j & 31);
-    if (lane == 0) issue(j, src);
   }
-  bool ok = true;
-  for (int j = 0; j < cnt; ++j) {
-    if ((j & 31) == 0 && j > 0) {            // entering the next batch of indices
-      cur_idx = nxt_idx;
-      nxt_idx = (j + 32 + lane < cnt) ? __ldcs(a.idx + it.begin + j + 32 + lane) : 0;
-    }
-    const int stage = j & smask;
-    ok = bar_wait(bars_s + 8 * stage, (uint32_t)((j >> stages_log2) & 1));
-    if (!__all_sync(FULL, ok)) {
-      ok = false;
-      break;
-    }
-    const uint4 *slot = reinterpret_cast<const uint4 *>(ring + (size_t)stage * slot_bytes);
-    uint4 raw[NV];
-#pragma unroll
-    for (int v = 0; v < NV; ++v) raw[v] = cok[v] ? slot[v * 32 + lane] : make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      uint64_t val[VP];
-      unpack_pairs<T>(raw[v], val);
-#pragma unroll
-      for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], v * VP + k);
-    }
-    // every lane has consumed its part of the slot (the adds above depend on the loads): refill it
-    const int jn = j + stages;
-    const int src = __shfl_sync(FULL, (jn >> 5) == (j >> 5) ? cur_idx : nxt_idx, jn & 31);
-    if (jn < cnt && lane == 0) issue(jn, src);
-  }
-  if (!ok) {
-    if (lane == 0) atomicAdd(&g_bulk_wait_timeouts, 1);
-    for (int s = 0; s < stages; ++s) bar_wait(bars_s + 8 * s, 0), bar_wait(bars_s + 8 * s, 1);   // bounded drain
-    return;
-  }
+  if (g != 0 || !cok) return;
 
   if (it.slot < 0) {
     T *y = static_cast<T *>(a.y) + (int64_t)it.row * a.F;
     const float scale = a.dst_scale ? __ldg(a.dst_scale + it.row) : 1.f;
+    float o[VEC];
 #pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      if (!cok[v]) continue;
-      float o[VEC];
+    for (int k = 0; k < VP; ++k) unpack2(acc[k].value(k), o[2 * k], o[2 * k + 1]);
 #pragma unroll
-      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(v * VP + k), o[2 * k], o[2 * k + 1]);
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
-        if (a.relu) o[k] = fmaxf(o[k], 0.f);
-      }
-      VecOf<T>::store(y + (int64_t)(v * 32 + lane) * VEC, o);
+    for (int k = 0; k < VEC; ++k) {
+      if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
+      if (a.relu) o[k] = fmaxf(o[k], 0.f);
     }
+    VecOf<T>::store(y + (int64_t)cv * VEC, o);
   } else {
     float *hi = a.scratch + (int64_t)(2 * it.slot) * a.plane;
     float *lo = hi + a.plane;
 #pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      if (!cok[v]) continue;
-#pragma unroll
-      for (int k = 0; k < VP; ++k) {
-        float h0, h1, l0, l1;
-        acc[v][k].planes(h0, h1, l0, l1, v * VP + k);
-        const int c = (v * 32 + lane) * VEC + 2 * k;
-        hi[c] = h0, hi[c + 1] = h1, lo[c] = l0, lo[c + 1] = l1;
-      }
+    for (int k = 0; k < VP; ++k) {
+      float h0, h1, l0, l1;
+      acc[k].planes(h0, h1, l0, l1, k);
+      hi[cv * VEC + 2 * k] = h0, hi[cv * VEC + 2 * k + 1] = h1;
+      lo[cv * VEC + 2 * k] = l0, lo[cv * VEC + 2 * k + 1] = l1;
     }
   }
 }
 
-template <typename T, int NV, int EXACT>
-static int launch_bulk_e(const GatherArgs &a, cudaStream_t stream) {
-  const uint32_t slot_bytes = ((uint32_t)a.FV * 16u + 127u) & ~127u;
-  int stages_log2 = 4;                                                  // up to 16 rows in flight per warp,
-  while (stages_log2 > 1 && (size_t)BULK_WARPS * (1 << stages_log2) * slot_bytes > 32 * 1024) --stages_log2;   // <= 32 KB per block
-  const int stages = 1 << stages_log2;
-  const size_t smem = (size_t)BULK_WARPS * stages * slot_bytes + (size_t)BULK_WARPS * stages * 8;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(gather_sum_bulk_kernel<T, NV, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(GPHL_ERR_CUDA, "gather_sum_bulk: shared memory opt-in: %s", cudaGetErrorString(e));
-  }
-  const unsigned grid = (unsigned)((a.n_items + BULK_WARPS - 1) / BULK_WARPS);
-  gather_sum_bulk_kernel<T, NV, EXACT><<<grid, BULK_WARPS * 32, smem, stream>>>(a, stages_log2);
-  return launched("gather_sum_bulk_kernel");
+template <typename T, int LPR>
+static int launch_sliced(const GatherArgs &a, cudaStream_t stream) {
+  dim3 grid((unsigned)((a.n_items + WARPS - 1) / WARPS), (unsigned)((a.FV + LPR - 1) / LPR));
+  if (a.exact) gather_sum_sliced_kernel<T, LPR, 3><<<grid, WARPS * 32, 0, stream>>>(a);
+  else gather_sum_sliced_kernel<T, LPR, 0><<<grid, WARPS * 32, 0, stream>>>(a);
+  return launched("gather_sum_sliced_kernel");
 }
 
-template <typename T, int NV>
-static int launch_bulk(const GatherArgs &a, cudaStream_t stream) {
-  return a.exact ? launch_bulk_e<T, NV, true>(a, stream) : launch_bulk_e<T, NV, false>(a, stream);
+// Slice width (in 16-byte vectors) for the unweighted sum, 0 = one pass over whole rows (the default: on the 62 M-edge,
+// 256-column gather one pass takes 6.1 ms, two slices 6.7 ms, four 8.2 ms, eight 14.5 ms: with a warp per item the
+// fixed cost of a short item is paid once per slice and outweighs the better cache hit rate).  Measurement builds
+// choose the width with GPHL_SLICE_LPR.
+static int slice_lanes(int32_t /*FV*/) {
+  const int forced = knob("GPHL_SLICE_LPR", 0);
+  return forced < 0 ? 0 : forced;
 }
 
 // Any shape / alignment: one thread per (item, column), serial over the piece.
@@ -733,12 +686,8 @@ static int launch_vec(const GatherArgs &a, cudaStream_t stream) {
   // Which exact accumulator: measured on the 62 M-edge, 256-column gather, the unweighted sum is fastest with the
   // columns split between the fp64 and the fp32 pipe (5.9 ms; two-sum alone 6.7, double alone 6.4), the edge-weighted
   // sum with doubles alone (7.8 ms against 9.4: its exact product is one fused multiply-add in double and ten
-  // operations in fp32); the attention aggregate does not care (it waits on its per-edge weights).  GPHL_ACC =
-  // twosum | f64 | mixed overrides the choice.
-  static const int forced = [] {
-    const char *e = getenv("GPHL_ACC");
-    return !e ? 0 : std::string(e) == "twosum" ? 1 : std::string(e) == "f64" ? 2 : std::string(e) == "mixed" ? 3 : 0;
-  }();
+  // operations in fp32); the attention aggregate does not care (it waits on its per-edge weights).  
+  const int forced = knob("GPHL_ACC", 0);            // measurement builds: 1 two-sum, 2 double, 3 mixed
   const int kind = forced ? forced : (MODE == MUL_E ? 2 : 3);
   if (kind == 1) return launch_vec_e<T, MODE, LPR, NV, 1>(a, stream);
   if (kind == 2) return launch_vec_e<T, MODE, LPR, NV, 2>(a, stream);
@@ -769,14 +718,12 @@ static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t
     a.wvec = 0;
     if (MODE == MUL_E) a.wvec = a.H % 4 == 0 && aligned16(a.w);
     if (MODE == GAT) a.wvec = a.H % 4 == 0 && aligned16(a.el) && aligned16(a.er) && aligned16(a.stats);
-    static const bool use_bulk = [] {
-      const char *e = getenv("GPHL_GATHER");
-      return e && std::string(e) == "bulk";
-    }();
-    if (MODE == COPY && use_bulk && a.FV >= 32 && a.FV <= 128) {
-      if (a.FV <= 32) rc = launch_bulk<T, 1>(a, stream);
-      else if (a.FV <= 64) rc = launch_bulk<T, 2>(a, stream);
-      else rc = launch_bulk<T, 4>(a, stream);
+    const int slice = (MODE == COPY) ? slice_lanes(a.FV) : 0;
+    if (MODE == COPY && slice > 0) {
+      if (slice >= 32) rc = launch_sliced<T, 32>(a, stream);
+      else if (slice >= 16) rc = launch_sliced<T, 16>(a, stream);
+      else if (slice >= 8) rc = launch_sliced<T, 8>(a, stream);
+      else rc = launch_sliced<T, 4>(a, stream);
     } else
     if (a.FV <= 1) rc = launch_vec<T, MODE, 1, 1>(a, stream);
     else if (a.FV <= 2) rc = launch_vec<T, MODE, 2, 1>(a, stream);

@@ -279,12 +279,20 @@ Tensor u_add_v_mul_alpha(Tensor l, Tensor r, int64_t /*alpha: ignored, as in the
   return z;
 }
 
-// Not registered by the reference (its HGT graph runs aten::mul + aten::sum on gathered rows).
+// Not registered by the reference (its HGT graph runs aten::mul + aten::sum on gathered rows).  Replaces
+// sum(mul(BroadcastSrcNode(l), BroadcastDstNode(r)), [1], keepdim): the kernel covers two-dimensional fp32 operands of
+// equal width; every other shape (trailing dimensions, widths that only broadcast, other dtypes) takes the unfused
+// route, so the rewrite never changes what a graph accepts or returns.
 Tensor u_dot_v(Tensor l, Tensor r, int64_t heads, const GraphPtr &g) {
-  Tensor lc = cuda_f32(l, "source features"), rc_ = cuda_f32(r, "destination features");
-  const int64_t f = feat_of(lc);
-  TORCH_CHECK(heads >= 1 && f % heads == 0 && feat_of(rc_) == f, "u_dot_v: bad feature widths");
-  TORCH_CHECK(lc.size(0) == g->num_nodes && rc_.size(0) == g->num_nodes, "u_dot_v: inputs must have num_nodes rows");
+  const bool fits = l.is_cuda() && r.is_cuda() && l.scalar_type() == torch::kFloat32 && r.scalar_type() == torch::kFloat32 &&
+                    l.dim() == 2 && r.dim() == 2 && l.size(0) == g->num_nodes && r.size(0) == g->num_nodes &&
+                    l.size(1) == r.size(1) && heads >= 1 && l.size(1) % heads == 0;
+  if (!fits) {
+    TORCH_CHECK(heads == 1, "gsddmm_u_dot_v: the general form needs heads == 1");
+    return at::sum(at::mul(gather_rows(l, g->COO_src, c10::nullopt), gather_rows(r, g->COO_dst, c10::nullopt)), {1}, true);
+  }
+  Tensor lc = l.contiguous(), rc_ = r.contiguous();
+  const int64_t f = lc.size(1);
   Tensor z = torch::empty({g->num_edges, heads}, lc.options());
   Tensor s = cuda_idx(g->COO_src, torch::kInt64, "COO_src"), d = cuda_idx(g->COO_dst, torch::kInt64, "COO_dst");
   c10::cuda::CUDAGuard guard(lc.device());

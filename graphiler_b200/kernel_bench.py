@@ -2,16 +2,23 @@
 
   python -m graphiler_b200.kernel_bench --config c2 --kernel copy_u_sum [--scale S] [--iters K]
                                         [--feat F] [--dtype fp32|bf16] [--chunk C] [--fast]
+                                        [--measure] [--sweep NAME=v1,v2,...]
 
 Times one kernel of the library with CUDA events (warm-up, then K launches) on a seeded synthetic
 graph of the chosen configuration and prints one JSON line with its time, its algorithmic bytes
 (every distinct input element once + every output element once + the index arrays once) and the
 resulting GB/s.  It is also the command the profiler captures are taken from.
+
+``--measure`` loads lib/libgphl_measure.so (``python -m graphiler_b200.build --measure``), the build whose tuning
+knobs are read from the environment; ``--sweep NAME=v1,v2,...`` then times the kernel once per value of that knob on
+the same graph and inputs (one JSON line each, with the largest difference of the output from the first value's).
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
+from pathlib import Path
 
 import torch
 
@@ -22,7 +29,7 @@ KERNELS = ("linear", "copy_u_sum", "copy_e_sum", "u_mul_e_sum", "u_add_v", "u_do
 
 
 def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: int, heads: int, dtype: str,
-        chunk: int, fast: bool = False, device: str = "cuda:0"):
+        chunk: int, fast: bool = False, device: str = "cuda:0", sweep=None):
     gen_dev = device if config == "c5" else "cpu"
     wl = synthetic.make(config, scale=scale, device=gen_dev).to(device)
     g = wl.graph
@@ -98,24 +105,43 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
     else:
         raise SystemExit(f"unknown kernel {kernel}")
 
-    for _ in range(warmup):
-        fn()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.profiler.start()               # a profiler started with --profile-from-start off sees only these launches
-    a.record()
-    for _ in range(iters):
-        fn()
-    b.record()
-    torch.cuda.synchronize()
-    torch.cuda.profiler.stop()
-    ms = a.elapsed_time(b) / iters
-    out = {"config": config, "kernel": kernel, "scale": scale, "nodes": n, "edges": e, "feat": feat, "heads": heads,
-           "dtype": dtype, "chunk": chunk, "fast_accum": fast, "ms": ms, "algorithmic_bytes": b_alg, "gbs": b_alg / ms / 1e6,
-           "split_rows": pg.plan_in(feat).num_split_rows, "items": pg.plan_in(feat).num_items}
-    if flops:
-        out["tflops"] = flops / ms / 1e9
-    return out
+    def timed():
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.profiler.start()           # a profiler started with --profile-from-start off sees only these launches
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        ms = a.elapsed_time(b) / iters
+        out = {"config": config, "kernel": kernel, "scale": scale, "nodes": n, "edges": e, "feat": feat, "heads": heads,
+               "dtype": dtype, "chunk": chunk, "fast_accum": fast, "ms": ms, "algorithmic_bytes": b_alg,
+               "gbs": b_alg / ms / 1e6, "split_rows": pg.plan_in(feat).num_split_rows, "items": pg.plan_in(feat).num_items}
+        if flops:
+            out["tflops"] = flops / ms / 1e9
+        return out
+
+    if not sweep:
+        return [timed()]
+    name, values = sweep
+    outs, first = [], None
+    for v in values:
+        os.environ[name] = v
+        res = fn()
+        res = res[0] if isinstance(res, tuple) else res
+        o = timed()
+        o["knob"] = {name: v}
+        if torch.is_tensor(res):
+            if first is None:
+                first = res.float().clone()
+            o["max_abs_diff_from_first"] = float((res.float() - first).abs().max())
+        outs.append(o)
+    os.environ.pop(name, None)
+    return outs
 
 
 def main():
@@ -130,8 +156,19 @@ def main():
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--chunk", type=int, default=capi.DEFAULT_CHUNK)
     ap.add_argument("--fast", action="store_true", help="plain fp32 accumulation instead of compensated")
+    ap.add_argument("--measure", action="store_true", help="load the measurement build of the kernel library")
+    ap.add_argument("--sweep", default=None, help="NAME=v1,v2,...: one timing per value of a tuning knob (needs --measure)")
     a = ap.parse_args()
-    print(json.dumps(run(a.config, a.kernel, a.scale, a.iters, a.warmup, a.feat, a.heads, a.dtype, a.chunk, a.fast)))
+    if a.measure:
+        capi.load_library(Path(capi.KERNEL_LIB).with_name("libgphl_measure.so"), make_default=True)
+    sweep = None
+    if a.sweep:
+        if not a.measure:
+            raise SystemExit("--sweep needs --measure")
+        name, vals = a.sweep.split("=", 1)
+        sweep = (name, vals.split(","))
+    for o in run(a.config, a.kernel, a.scale, a.iters, a.warmup, a.feat, a.heads, a.dtype, a.chunk, a.fast, sweep=sweep):
+        print(json.dumps(o), flush=True)
 
 
 if __name__ == "__main__":

@@ -90,4 +90,6 @@ def build(ref: Path) -> int:
 
 
 if __name__ == "__main__":
-    sys.exit(build(Path(sys.argv[1]) if len(sys.argv) > 1 and not sys.argv[1].startswith("smoke") else Path("/root/reference")))
+    import os
+    default = Path(os.environ.get("GRAPHILER_REFERENCE_DIR", HERE.parent.parent / "reference"))
+    sys.exit(build(Path(sys.argv[1]) if len(sys.argv) > 1 else default))

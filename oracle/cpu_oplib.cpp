@@ -117,6 +117,8 @@ static Tensor SegmentMMEdge(Tensor x, Tensor w, const G &g) { return segment_mm(
 // ---- operators the reference does not register: the targets of the added fusion patterns, restated as the
 // unfused chains they replace so that a rewritten graph can be checked on the CPU -------------------------------
 static Tensor u_dot_v(Tensor l, Tensor r, int64_t heads, const G &g) {
+  if (l.dim() != 2 || r.dim() != 2 || l.size(1) != r.size(1))      // the chain the rewrite replaced, literally
+    return at::mul(l.index_select(0, g->COO_src), r.index_select(0, g->COO_dst)).sum({1}, true);
   auto a = two_d(l).index_select(0, g->COO_src), b = two_d(r).index_select(0, g->COO_dst);
   return (a * b).reshape({a.size(0), heads, -1}).sum(2);
 }

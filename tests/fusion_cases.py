@@ -37,6 +37,18 @@ def u_dot_v_case(g: G, a: torch.Tensor, b: torch.Tensor):
     return torch.sum(d * s, [1], True)
 
 
+def u_dot_v_three_dims(g: G, a: torch.Tensor, b: torch.Tensor):        # (N, H, D) operands: the sum runs over H only
+    s = torch.ops.my_ops.BroadcastSrcNode(a, g)
+    d = torch.ops.my_ops.BroadcastDstNode(b, g)
+    return torch.sum(s * d, [1], True)
+
+
+def u_dot_v_broadcast_width(g: G, a: torch.Tensor, b: torch.Tensor):   # (N, F) x (N, 1)
+    s = torch.ops.my_ops.BroadcastSrcNode(a, g)
+    d = torch.ops.my_ops.BroadcastDstNode(b, g)
+    return torch.sum(s * d, [1], True)
+
+
 def dot_without_keepdim(g: G, a: torch.Tensor, b: torch.Tensor):
     s = torch.ops.my_ops.BroadcastSrcNode(a, g)
     d = torch.ops.my_ops.BroadcastDstNode(b, g)
@@ -101,6 +113,9 @@ def main():
     rn = lambda *s: torch.randn(*s, generator=gen).to(dev)
     cases = [
         ("u_dot_v", u_dot_v_case, (rn(n, 16), rn(n, 16)), {"gsddmm_u_dot_v": 1}),
+        # shapes the fused kernel does not cover: the operator must return what the unfused chain returned
+        ("u_dot_v_three_dims", u_dot_v_three_dims, (rn(n, 2, 8), rn(n, 2, 8)), {"gsddmm_u_dot_v": 1}),
+        ("u_dot_v_broadcast_width", u_dot_v_broadcast_width, (rn(n, 16), rn(n, 1)), {"gsddmm_u_dot_v": 1}),
         ("dot_without_keepdim", dot_without_keepdim, (rn(n, 16), rn(n, 16)), {}),
         ("dot_with_second_reader", dot_with_second_reader, (rn(n, 16), rn(n, 16)), {}),
         ("attention_relu", attention_relu, (rn(n, 1), rn(n, 1), rn(n, 16)), {"gat_fused": 1}),
