@@ -103,35 +103,83 @@ def env_world():
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU arm: the restated user-defined-function path on a bounded destination-row slice
+# CPU arm.  Two figures, both on the host cores of the machine the bench runs on:
+#  * the timed baseline: one whole GCN layer on the whole graph, measured in full every step and never scaled:
+#    torch.mm for the projection (all threads) and the compiled destination-row loop of oracle/csr_cpu.c (OpenMP,
+#    float sums in ascending position order: the reference kernels' arithmetic) for scale -> gather-sum -> scale -> relu;
+#  * beside it, the restated user-defined-function path (edge-id-order message pass, degree-bucketed mailbox reduce)
+#    on the first destination rows holding 1/16 of the edges (the R-MAT hubs are among them), labelled as
+#    extrapolated with its scale factor: run in full it materialises 61 GB of messages.
 
-def cpu_reference_sample(g_cpu, x_cpu, w_cpu, target_edges: int, threads: int):
-    """One GCN layer on the host: the full dense projection plus message/reduce over a slice of
-    destination rows holding about ``target_edges`` in-edges; returns (seconds scaled to the whole
-    graph, description, slice output rows, row range)."""
-    from oracle import udf_oracle as U
-    torch.set_num_threads(threads)
-    n, e = g_cpu.num_nodes, g_cpu.num_edges
-    ptr = g_cpu.in_pointer.to(torch.int64)
-    r0 = n // 3
-    stop = int(torch.searchsorted(ptr, ptr[r0] + min(target_edges, e)).clamp(max=n))
-    r1 = max(r0 + 1, stop)
-    e_slice = int(ptr[r1] - ptr[r0])
-    deg = g_cpu.in_degrees().clamp(min=1).float()
-    norm = deg.pow(-0.5).unsqueeze(1)
-    t0 = time.perf_counter()
-    h = torch.mm(x_cpu, w_cpu)
-    t_mm = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    out = U.update_all(g_cpu, {"h": h, "norm": norm, "norm_dst": norm}, {}, {}, {},
-                       lambda ed: {"m": ed.src["h"] * ed.src["norm"]},
-                       lambda nd: {"h": torch.relu(torch.sum(nd.mailbox["m"], dim=1) * nd.data["norm_dst"])},
-                       rows=range(r0, r1))["h"]
-    t_udf = time.perf_counter() - t0
-    scaled = t_mm + t_udf * (e / max(1, e_slice))
-    desc = (f"full X@W ({n}x{x_cpu.shape[1]}x{w_cpu.shape[1]}) + message/reduce over destination rows "
-            f"[{r0},{r1}) = {e_slice} of {e} edges, message/reduce time scaled by {e / max(1, e_slice):.1f}")
-    return scaled, desc, out, (r0, r1)
+class CpuLayer:
+    def __init__(self, g_cpu, x_cpu, w_cpu, threads: int):
+        from oracle import csr_cpu as K
+        self.K, self.g, self.x, self.w, self.threads = K, g_cpu, x_cpu, w_cpu, threads
+        torch.set_num_threads(threads)
+        K.set_threads(threads)
+        self.ptr = g_cpu.in_pointer.numpy()
+        self.idx = g_cpu.in_node_indices.numpy()
+        deg = g_cpu.in_degrees().clamp(min=1).float()
+        self.norm = deg.pow(-0.5)
+        self.out = None
+
+    def step(self):
+        """One whole layer; returns (seconds, seconds of the projection)."""
+        import numpy as np
+        t0 = time.perf_counter()
+        h = torch.mm(self.x, self.w)
+        h.mul_(self.norm.unsqueeze(1))
+        t1 = time.perf_counter()
+        if self.out is None:
+            self.out = np.empty((self.g.num_nodes, h.shape[1]), dtype=np.float32)
+        self.K.gather_sum_f32(self.ptr, self.idx, h.numpy(), dst_scale=self.norm.numpy(), relu=True, out=self.out)
+        t2 = time.perf_counter()
+        return t2 - t0, t1 - t0
+
+    def describe(self):
+        n, e = self.g.num_nodes, self.g.num_edges
+        return (f"whole layer on the whole graph each step, not scaled: torch.mm {n}x{self.x.shape[1]}x{self.w.shape[1]} + "
+                f"compiled destination-row loop over all {e} edges (oracle/csr_cpu.c, OpenMP, float sums)")
+
+    def udf_slice(self, fraction: float):
+        """The restated UDF path on destination rows [0, r1) holding about `fraction` of the edges."""
+        from oracle import udf_oracle as U
+        g = self.g
+        n, e = g.num_nodes, g.num_edges
+        ptr = g.in_pointer.to(torch.int64)
+        r1 = int(torch.searchsorted(ptr, torch.tensor(int(e * fraction))).clamp(min=1, max=n))
+        e_slice = int(ptr[r1])
+        norm = self.norm.unsqueeze(1)
+        t0 = time.perf_counter()
+        h = torch.mm(self.x, self.w)
+        t_mm = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        U.update_all(g, {"h": h, "norm": norm, "norm_dst": norm}, {}, {}, {},
+                     lambda ed: {"m": ed.src["h"] * ed.src["norm"]},
+                     lambda nd: {"h": torch.relu(torch.sum(nd.mailbox["m"], dim=1) * nd.data["norm_dst"])},
+                     rows=range(0, r1))
+        t_udf = time.perf_counter() - t0
+        factor = e / max(1, e_slice)
+        return {"value": 1e3 * (t_mm + t_udf * factor), "unit": "ms", "extrapolated": True, "scale_factor": factor,
+                "measured_ms": {"projection_full": 1e3 * t_mm, "message_reduce_slice": 1e3 * t_udf},
+                "sample": f"destination rows [0,{r1}) = {e_slice} of {e} edges (largest in-degree in the slice "
+                          f"{int((ptr[1:r1 + 1] - ptr[:r1]).max())}); message/reduce time x {factor:.2f}, projection in full"}
+
+
+def reference_gpu_ops(scale: float):
+    """Device times of the reference's own CUDA operators on this machine (its unmodified sources built by
+    oracle/build_ref_cuda.py), from a child process: their library registers the same operator names as this one."""
+    script = ROOT / "oracle" / "time_ref_ops.py"
+    if not (ROOT / "oracle" / "_ref" / "libgraphiler_ref.so").exists() or not script.exists():
+        return {"unavailable": "oracle/_ref/libgraphiler_ref.so is not built"}
+    try:
+        r = subprocess.run([sys.executable, str(script), "--scale", str(scale)], capture_output=True, text=True, timeout=600)
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        if r.returncode != 0 or not lines:
+            return {"unavailable": (r.stderr or r.stdout)[-300:]}
+        return json.loads(lines[-1])
+    except Exception as ex:  # noqa: BLE001
+        return {"unavailable": repr(ex)[:300]}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -145,18 +193,21 @@ def run_reference(args):
     g_cpu, x_cpu, w_cpu = wl.graph.to("cpu"), wl.feats.cpu(), wl.params["gcn_w"].cpu()
     del wl
     threads = os.cpu_count() or 1
-    target = max(1000, int(g_cpu.num_edges * args.cpu_fraction))
-    times, desc = [], ""
+    cpu = CpuLayer(g_cpu, x_cpu, w_cpu, threads)
+    times, mm = [], []
     for i in range(args.warmup + args.steps):
-        t, desc, _, _ = cpu_reference_sample(g_cpu, x_cpu, w_cpu, target, threads)
+        t, t_mm = cpu.step()
         if i >= args.warmup:
-            times.append(t)
+            times.append(t), mm.append(t_mm)
     ms = 1e3 * sum(times) / len(times)
+    cfg = workload_config(g_cpu, args, 1)
+    cfg["accumulation"] = "fp32 plain, ascending position order"
     line = {"impl": "reference", "metric": "gcn_layer_fwd_ms", "value": ms, "unit": "ms", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(g_cpu, args, 1),
-            "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": desc},
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+            "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": cpu.describe(),
+                             "extrapolated": False, "projection_ms": 1e3 * sum(mm) / len(mm),
+                             "udf_path": cpu.udf_slice(args.cpu_fraction)},
             "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
@@ -171,6 +222,46 @@ def workload_config(g, args, world):
                           if args.exchange == "allgather" else f"dst-rows x{world} (edge-balanced) + halo all-to-all of the rows each shard reads, source rows "
                           + ("dealt to the ranks by a hash of their id" if args.ownership != "blocks" else "owned in contiguous blocks")),
             "l2": "inputs (2.4 GB features, 0.25 GB indices) exceed the 126 MB L2; no flush between steps"}
+
+
+def check_step(g_cpu, x_cpu, w_cpu, sl, step, out, dtype):
+    """Parity of one step at the bench's own size (single GPU): the aggregation of EVERY destination row against
+    the double-precision destination-row loop of oracle/csr_cpu.c fed with the projected rows the GPU produced
+    (|err| <= 1e-6 + 1e-5 |truth|; one bf16 rounding more for bf16 storage), and the projection on sampled rows
+    against a double-precision product (the same bound plus 2 ulp of sum |x||w|, the tensor-core allowance).
+    Raises if either is outside its bound: a fast wrong step must not print a bench line."""
+    import numpy as np
+    from oracle import csr_cpu as K
+    from graphiler_b200 import layers
+    n = g_cpu.num_nodes
+    deg = g_cpu.in_degrees().clamp(min=1).float()
+    norm = deg.pow(-0.5)
+    # on one GPU the layer's persistent buffer holds the projected source rows in node order
+    if not torch.equal(sl.shard.node_indices.cpu(), g_cpu.in_node_indices):
+        return {"checked": False, "why": "the projected rows are not kept in node order by this exchange"}
+    h = sl.gathered[:n].float().cpu().numpy()
+    got = out.float().cpu().numpy()
+    ptr, idx = g_cpu.in_pointer.numpy(), g_cpu.in_node_indices.numpy()
+    bad, worst, blk = 0, 0.0, 200_000
+    rel = 1e-5 if dtype == torch.float32 else 2.0 ** -8
+    for r0 in range(0, n, blk):
+        r1 = min(n, r0 + blk)
+        truth = K.gather_sum_f64(ptr, idx, h, dst_scale=norm.numpy(), relu=True, rows=(r0, r1))
+        err = np.abs(got[r0:r1].astype(np.float64) - truth)
+        bad += int((err > 1e-6 + rel * np.abs(truth)).sum())
+        worst = max(worst, float(err.max()) if err.size else 0.0)
+    rows = torch.randperm(n, generator=torch.Generator().manual_seed(3))[:20000]
+    xs, ws = x_cpu[rows].double(), w_cpu.double()
+    truth = (xs @ ws) * norm[rows].double().unsqueeze(1)
+    allow = 1e-6 + rel * truth.abs() + 2 * 2.0 ** -23 * (xs.abs() @ ws.abs()) * norm[rows].double().unsqueeze(1)
+    perr = (torch.from_numpy(h)[rows].double() - truth).abs()
+    pbad = int((perr > allow).sum())
+    res = {"checked": True, "aggregate_rows": n, "aggregate_out_of_bound": bad, "aggregate_max_abs_err": worst,
+           "projection_rows": int(rows.numel()), "projection_out_of_bound": pbad,
+           "projection_max_abs_err": float(perr.max()), "bound": f"1e-6 + {rel:g} |truth|"}
+    if bad or pbad:
+        raise SystemExit("bench.py: the step's output is outside the parity bound: " + json.dumps(res))
+    return res
 
 
 def time_loop(fn, steps, warmup, sync):
@@ -503,14 +594,25 @@ def run_native(args):
             # re-reads a source row once per edge; what L2 does not absorb is DRAM traffic the kernel cannot avoid)
             line["roofline"]["traffic_gbs"] = line["roofline"]["traffic"] / k_ms_max / 1e6
             line["roofline"]["traffic_frac"] = line["roofline"]["traffic_gbs"] / hbm
+    # What the step returned, as one 64-bit number that does not depend on how the rows are split over the ranks:
+    # the sum of the output's bit patterns (integer addition is associative, so every N must print the same value).
+    bits = out.view(torch.int32 if out.dtype == torch.float32 else torch.int16).to(torch.int64)
+    csum = bits.sum().reshape(1)
+    if world > 1:
+        dist.all_reduce(csum, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        line["output_checksum"] = f"{int(csum.item()) & 0xFFFFFFFFFFFFFFFF:016x}"
     if g_cpu is not None:
+        line["parity"] = check_step(g_cpu, x_cpu, w.cpu(), sl, step, out, dtype)
         threads = os.cpu_count() or 1
-        target = max(1000, int(e * args.cpu_fraction))
-        sec, desc, ref_rows, (c0, c1) = cpu_reference_sample(g_cpu, x_cpu, w.cpu(), target, threads)
-        got = out[c0:c1].float().cpu()
-        err = (got - ref_rows).abs().max().item()
-        line["cpu_baseline"] = {"value": sec * 1e3, "unit": "ms", "cores": threads, "kind": "port", "sample": desc,
-                                "max_abs_diff_vs_gpu_on_sample_rows": err}
+        cpu = CpuLayer(g_cpu, x_cpu, w.cpu(), threads)
+        cpu.step()
+        sec, sec_mm = cpu.step()
+        line["cpu_baseline"] = {"value": sec * 1e3, "unit": "ms", "cores": threads, "kind": "port", "sample": cpu.describe(),
+                                "extrapolated": False, "projection_ms": sec_mm * 1e3,
+                                "udf_path": cpu.udf_slice(args.cpu_fraction),
+                                "reference_gpu_ops_ms": reference_gpu_ops(args.scale)}
+        del cpu
     if rank == 0 and world == 1 and not args.no_extras:
         del sl, out, x_blk
         torch.cuda.empty_cache()
@@ -531,7 +633,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (testing only)")
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
-    ap.add_argument("--cpu-fraction", type=float, default=1.0 / 64, help="share of the edges in the CPU sample")
+    ap.add_argument("--cpu-fraction", type=float, default=1.0 / 16,
+                    help="share of the edges in the slice the restated user-defined-function path is timed on")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-config layer timings")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--ownership", default="auto", choices=["auto", "blocks", "hashed"],

@@ -29,6 +29,10 @@ SIGNATURES = {
     "gphl_version": (c_int, []),
     "gphl_launch_count": (c_int64, []),
     "gphl_plan_create": (c_int, [_P, c_int64, c_int32, c_int64, _P, POINTER(_P)]),
+    "gphl_plan_bind_scratch": (c_int, [_P, _P, c_int64]),
+    "gphl_plan_num_pieces": (c_int64, [_P]),
+    "gphl_validate_csr": (c_int, [_P, c_int64, c_int64, _P, c_int64, _P, c_int64, _P]),
+    "gphl_validate_index_i64": (c_int, [_P, c_int64, c_int64, _P]),
     "gphl_plan_destroy": (None, [_P]),
     "gphl_plan_num_items": (c_int64, [_P]),
     "gphl_plan_num_split_rows": (c_int64, [_P]),
@@ -42,6 +46,7 @@ SIGNATURES = {
     "gphl_sddmm_u_add_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_sddmm_u_dot_v_f32_i64": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_sddmm_u_dot_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_sddmm_u_dot_v_csc_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_segment_softmax_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_segment_softmax_noalloc_f32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
     "gphl_gat_fused_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, c_float, _P, _P, _P, _P]),
@@ -168,6 +173,23 @@ class Plan:
             pass
 
 
+def validate_csr(pointer, idx, idx_limit: int, edge_idx=None, edge_limit: int = 0) -> None:
+    """Raise GphlError unless `pointer` is a non-decreasing array from 0 to len(idx) and every index is in range
+    (one pass on the device; synchronises).  The kernels themselves trust these arrays."""
+    _dev(pointer, idx, edge_idx)
+    with torch.cuda.device(pointer.device):
+        _check(lib().gphl_validate_csr(_ptr(pointer), pointer.numel() - 1, idx.numel(), _ptr(idx), idx_limit,
+                                       _ptr(edge_idx), edge_limit, _stream(pointer)), "validate_csr")
+
+
+def validate_index(index, limit: int) -> None:
+    """Raise GphlError unless every value of the int64 array lies in [0, limit)."""
+    _dev(index)
+    assert index.dtype == torch.int64
+    with torch.cuda.device(index.device):
+        _check(lib().gphl_validate_index_i64(_ptr(index), index.numel(), limit, _stream(index)), "validate_index")
+
+
 def _h(plan: Optional[Plan]):
     return None if plan is None else plan.handle
 
@@ -230,6 +252,19 @@ def sddmm_u_dot_v(src, dst, l, r, heads: int, out=None):
     return z
 
 
+def sddmm_u_dot_v_csc(pointer, idx, edge_idx, l, r, heads: int, plan: Optional[Plan] = None, out=None):
+    """u_dot_v walked in destination-row order: out[edge_idx[i], h] = sum_d l[idx[i], h, d] * r[v, h, d] for every
+    position i of row v (``edge_idx`` None: edge id == position).  Raises GphlError for shapes only the COO form covers."""
+    _dev(pointer, idx, edge_idx, l, r, out)
+    n_rows, e, f = pointer.numel() - 1, idx.numel(), _feat(l)
+    z = out if out is not None else torch.empty((e, heads), dtype=torch.float32, device=l.device)
+    with torch.cuda.device(l.device):
+        _check(lib().gphl_sddmm_u_dot_v_csc_f32(_h(plan), _ptr(pointer), _ptr(idx, pointer), _ptr(edge_idx), n_rows, heads,
+                                                f // heads, _ptr(l, pointer), _ptr(r, pointer), _ptr(z, pointer),
+                                                _stream(l)), "sddmm_u_dot_v_csc")
+    return z
+
+
 def segment_softmax(pointer, edge_idx, x, plan: Optional[Plan] = None, out=None, stats=None):
     _dev(pointer, edge_idx, x, out, stats)
     n_rows, heads = pointer.numel() - 1, _feat(x)
@@ -250,6 +285,8 @@ def segment_softmax_noalloc(pointer, edge_idx, x, out):
     tensor too, and ``rows * heads`` must not exceed ``SOFTMAX_NOALLOC_MAX_ROW_HEADS``.  For callers
     that cannot obtain device memory at call time; calls on one device must not overlap."""
     _dev(pointer, edge_idx, x, out)
+    if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
+        raise GphlError("segment_softmax_noalloc: `out` must be a contiguous tensor of x's shape and dtype")
     n_rows, heads = pointer.numel() - 1, _feat(x)
     with torch.cuda.device(x.device):
         _check(lib().gphl_segment_softmax_noalloc_f32(_ptr(pointer), _ptr(edge_idx, pointer), n_rows, heads,

@@ -1,6 +1,8 @@
 // Host side of the library: error state, launch counter and the row-split plan.
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -41,7 +43,7 @@ extern "C" int gphl_plan_create(const int32_t *pointer, int64_t n_rows, int32_t 
   *out_plan = nullptr;
   GPHL_REQUIRE(pointer != nullptr && n_rows >= 0, "plan_create: bad pointer array");
   GPHL_REQUIRE(chunk >= 32 && chunk % 32 == 0, "plan_create: chunk must be a positive multiple of 32");
-  GPHL_REQUIRE(max_feat >= 1, "plan_create: max_feat must be >= 1");
+  GPHL_REQUIRE(max_feat >= 0, "plan_create: max_feat must be >= 0");
   GPHL_REQUIRE(n_rows < INT32_MAX, "plan_create: row count must fit int32");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
@@ -123,6 +125,90 @@ extern "C" void gphl_plan_destroy(gphl_plan *p) {
   delete p;
 }
 
+// Scratch handed in by the caller (2 * num_pieces * round_up(max_feat, 8) floats, 16-byte aligned) in place of scratch
+// the plan owns: a plan created with max_feat = 0 owns none, and a caller with its own allocator binds a buffer wide
+// enough for the next calls.  Not thread-safe against calls that use the plan at the same time.
+extern "C" int gphl_plan_bind_scratch(gphl_plan *p, void *scratch, int64_t max_feat) {
+  GPHL_REQUIRE(p != nullptr && max_feat >= 0, "plan_bind_scratch: bad arguments");
+  GPHL_REQUIRE(p->n_pieces == 0 || max_feat == 0 || (scratch != nullptr && aligned16(scratch)),
+               "plan_bind_scratch: scratch must be a 16-byte aligned device buffer");
+  if (p->owns_scratch && p->scratch) GPHL_CUDA(cudaFree(p->scratch));
+  p->owns_scratch = false;
+  p->scratch = static_cast<float *>(scratch);
+  p->max_feat = (max_feat + 7) / 8 * 8;
+  p->scratch_bytes = (int64_t)sizeof(float) * 2 * p->n_pieces * p->max_feat;
+  return GPHL_OK;
+}
+extern "C" int64_t gphl_plan_num_pieces(const gphl_plan *p) { return p ? p->n_pieces : 0; }
 extern "C" int64_t gphl_plan_num_items(const gphl_plan *p) { return p ? p->n_items : 0; }
 extern "C" int64_t gphl_plan_num_split_rows(const gphl_plan *p) { return p ? p->n_split_rows : 0; }
 extern "C" int64_t gphl_plan_scratch_bytes(const gphl_plan *p) { return p ? p->scratch_bytes : 0; }
+
+// ---- index validation ------------------------------------------------------------------------------------------------
+// The kernels trust the graph arrays (an index out of range is an out-of-bounds read).  These entry points check them
+// once per graph, where the arrays enter the library: the reference checks nothing (src/dglgraph.cpp:5-24) and a
+// memory checker cannot be assumed at the caller's site.  Each runs one pass over the array, synchronises the stream
+// and returns GPHL_ERR_INVALID_ARGUMENT with a message that names the first kind of violation found.
+namespace gphl {
+__device__ int g_check_flags[4];
+
+__global__ void check_pointer_kernel(const int32_t *__restrict__ ptr, int64_t n_rows, int64_t total, int *flags) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_rows && ptr[i + 1] < ptr[i]) flags[0] = 1;
+  if (i == 0 && (ptr[0] != 0 || (int64_t)ptr[n_rows] != total)) flags[1] = 1;
+}
+template <typename I>
+__global__ void check_range_kernel(const I *__restrict__ a, int64_t n, int64_t limit, int *flag) {
+  bool bad = false;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    bad |= a[i] < 0 || (int64_t)a[i] >= limit;
+  if (bad) *flag = 1;
+}
+static std::mutex g_check_mutex;
+
+template <typename I>
+static void launch_range(const I *a, int64_t n, int64_t limit, int *flag, cudaStream_t stream) {
+  if (n == 0 || a == nullptr) return;
+  const unsigned grid = (unsigned)std::min<int64_t>((n + 255) / 256, 148 * 16);
+  check_range_kernel<I><<<grid, 256, 0, stream>>>(a, n, limit, flag);
+}
+}  // namespace gphl
+
+extern "C" int gphl_validate_csr(const int32_t *pointer, int64_t n_rows, int64_t n_entries, const int32_t *idx,
+                                 int64_t idx_limit, const int32_t *eidx, int64_t eidx_limit, void *stream_) {
+  GPHL_REQUIRE(n_rows >= 0 && n_entries >= 0 && n_rows < INT32_MAX && n_entries < INT32_MAX, "validate: sizes out of range");
+  GPHL_REQUIRE(pointer != nullptr, "validate: pointer array is NULL");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  std::lock_guard<std::mutex> lock(g_check_mutex);
+  int *flags = nullptr;
+  GPHL_CUDA(cudaGetSymbolAddress((void **)&flags, g_check_flags));
+  GPHL_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * 4, stream));
+  check_pointer_kernel<<<(unsigned)(n_rows / 256 + 1), 256, 0, stream>>>(pointer, n_rows, n_entries, flags);
+  launch_range<int32_t>(idx, n_entries, idx_limit, flags + 2, stream);
+  launch_range<int32_t>(eidx, n_entries, eidx_limit, flags + 3, stream);
+  int h[4] = {0, 0, 0, 0};
+  GPHL_CUDA(cudaMemcpyAsync(h, flags, sizeof(h), cudaMemcpyDeviceToHost, stream));
+  GPHL_CUDA(cudaStreamSynchronize(stream));
+  GPHL_CUDA(cudaGetLastError());
+  if (h[0]) return fail(GPHL_ERR_INVALID_ARGUMENT, "validate: the pointer array decreases somewhere");
+  if (h[1]) return fail(GPHL_ERR_INVALID_ARGUMENT, "validate: the pointer array must start at 0 and end at %lld", (long long)n_entries);
+  if (h[2]) return fail(GPHL_ERR_INVALID_ARGUMENT, "validate: a neighbour index lies outside [0, %lld)", (long long)idx_limit);
+  if (h[3]) return fail(GPHL_ERR_INVALID_ARGUMENT, "validate: an edge index lies outside [0, %lld)", (long long)eidx_limit);
+  return GPHL_OK;
+}
+
+extern "C" int gphl_validate_index_i64(const int64_t *a, int64_t n, int64_t limit, void *stream_) {
+  GPHL_REQUIRE(n >= 0 && (a != nullptr || n == 0), "validate: bad arguments");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  std::lock_guard<std::mutex> lock(g_check_mutex);
+  int *flags = nullptr;
+  GPHL_CUDA(cudaGetSymbolAddress((void **)&flags, g_check_flags));
+  GPHL_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * 4, stream));
+  launch_range<int64_t>(a, n, limit, flags, stream);
+  int h = 0;
+  GPHL_CUDA(cudaMemcpyAsync(&h, flags, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  GPHL_CUDA(cudaStreamSynchronize(stream));
+  GPHL_CUDA(cudaGetLastError());
+  if (h) return fail(GPHL_ERR_INVALID_ARGUMENT, "validate: an index lies outside [0, %lld)", (long long)limit);
+  return GPHL_OK;
+}

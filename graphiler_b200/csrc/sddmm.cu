@@ -135,6 +135,91 @@ static int launch_u_dot_v_rows(const I *src, const I *dst, int64_t n_edges, int6
   return launched("u_dot_v_rows_kernel");
 }
 
+// u_dot_v in destination-row (CSC) order.  The COO kernels above fetch both endpoint rows for every edge; walking the
+// destination segments instead, a warp takes one work item of the row-split plan, keeps its destination row r[v] in
+// registers (half of each vector widened to double once, the other half as packed fp32 pairs), and gathers only the
+// source rows l[src]: half the gathered bytes, and half the conversions of the exact products.  Results go to
+// z[edge id] (scattered by the row's edge ids; contiguous when edge ids are destination-sorted).  Pieces of a cut
+// row need no combination: every edge's output is independent.  Lane layout as in u_dot_v_rows_kernel.
+template <int LPR, int NV>
+__global__ void __launch_bounds__(256) u_dot_v_csc_kernel(const Item *__restrict__ items, int64_t n_items,
+                                                          const int32_t *__restrict__ pointer,
+                                                          const int32_t *__restrict__ idx, const int32_t *__restrict__ eidx,
+                                                          int32_t H, int32_t FV, int32_t DV, const float4 *__restrict__ l,
+                                                          const float4 *__restrict__ r, float *__restrict__ z) {
+  constexpr int G = 32 / LPR, U = (NV >= 2) ? 2 : 4;
+  const int lane = threadIdx.x & 31, g = lane / LPR, ll = lane % LPR;
+  const int64_t item_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (item_id >= n_items) return;
+  const Item it = fetch_item(items, pointer, item_id);
+  const int cv0 = ll * NV;
+  const bool cok = cv0 < FV;
+  const int lanes_per_head = DV / NV;
+  double rd[NV][2];
+  uint64_t rp[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const float4 q = cok ? __ldg(r + (int64_t)it.row * FV + cv0 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    rd[v][0] = (double)q.x, rd[v][1] = (double)q.y;
+    rp[v] = pack2(q.z, q.w);
+  }
+  int next_idx = 0, next_eid = 0;
+  if (it.begin + lane < it.end) {
+    next_idx = __ldg(idx + it.begin + lane);
+    next_eid = eidx ? __ldg(eidx + it.begin + lane) : it.begin + lane;
+  }
+  for (int base = it.begin; base < it.end; base += 32) {
+    const int n = min(32, it.end - base);
+    const int my_idx = next_idx, my_eid = next_eid;
+    if (base + 32 + lane < it.end) {
+      next_idx = __ldg(idx + base + 32 + lane);
+      next_eid = eidx ? __ldg(eidx + base + 32 + lane) : base + 32 + lane;
+    }
+#pragma unroll 1
+    for (int jj = 0; jj < n; jj += G * U) {
+      float4 a[U][NV];
+      int e[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        e[u] = jj + u * G + g;
+        const int64_t s_row = __shfl_sync(FULL, my_idx, e[u] & 31);
+        const bool ok = e[u] < n && cok;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) a[u][v] = ok ? __ldg(l + s_row * FV + cv0 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        double accd = 0.0;
+        Acc2 acc2{0, 0};
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          accd = fma((double)a[u][v].x, rd[v][0], accd), accd = fma((double)a[u][v].y, rd[v][1], accd);
+          acc2.fma_exact(pack2(a[u][v].z, a[u][v].w), rp[v]);
+        }
+        float h0, h1, l0, l1;
+        unpack2(acc2.hi, h0, h1);
+        unpack2(acc2.lo, l0, l1);
+        double acc = accd + (((double)h0 + (double)h1) + ((double)l0 + (double)l1));
+        for (int off = 1; off < lanes_per_head; off <<= 1) acc += __shfl_xor_sync(FULL, acc, off);
+        const int64_t eid = __shfl_sync(FULL, my_eid, e[u] & 31);
+        if (e[u] < n && cok && (ll % lanes_per_head) == 0) z[eid * H + cv0 / DV] = (float)acc;
+      }
+    }
+  }
+}
+
+template <int LPR, int NV>
+static int launch_u_dot_v_csc(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx, const int32_t *eidx,
+                              int64_t n_rows, int64_t heads, int64_t fv, int64_t dv, const float *l, const float *r,
+                              float *z, cudaStream_t stream) {
+  const int64_t n_items = plan ? plan->n_items : n_rows;
+  if (n_items == 0) return GPHL_OK;
+  u_dot_v_csc_kernel<LPR, NV><<<(unsigned)((n_items + 7) / 8), 256, 0, stream>>>(
+      plan ? plan->items : nullptr, n_items, pointer, idx, eidx, (int32_t)heads, (int32_t)fv, (int32_t)dv,
+      reinterpret_cast<const float4 *>(l), reinterpret_cast<const float4 *>(r), z);
+  return launched("u_dot_v_csc_kernel");
+}
+
 static unsigned grid_for(int64_t total, int block) {
   int64_t g = (total + block - 1) / block;
   const int64_t cap = 148LL * 64;  // grid-stride beyond a few waves of the 148 SMs
@@ -216,6 +301,39 @@ extern "C" int gphl_sddmm_u_dot_v_f32_i64(const int64_t *src, const int64_t *dst
 extern "C" int gphl_sddmm_u_dot_v_f32_i32(const int32_t *src, const int32_t *dst, int64_t n_edges, int64_t heads,
                                           int64_t dim, const float *l, const float *r, float *z, void *stream) {
   return u_dot_v<int32_t>(src, dst, n_edges, heads, dim, l, r, z, stream);
+}
+
+// Destination-row order: out[eid[i], h] = sum_d l[idx[i], h, d] * r[v, h, d] for every position i of row v.
+// Returns GPHL_ERR_UNSUPPORTED for shapes the row kernel does not cover (the caller then uses the COO form).
+extern "C" int gphl_sddmm_u_dot_v_csc_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx,
+                                          const int32_t *eidx, int64_t n_rows, int64_t heads, int64_t dim, const float *l,
+                                          const float *r, float *z, void *stream_) {
+  GPHL_REQUIRE(n_rows >= 0 && n_rows < INT32_MAX && heads >= 1 && dim >= 1 && heads * dim < (1 << 20), "bad sizes");
+  if (n_rows == 0) return GPHL_OK;
+  GPHL_REQUIRE(pointer && idx && l && r && z, "null pointer argument");
+  GPHL_REQUIRE(!plan || plan->n_rows == n_rows, "plan was built for a different row count");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int64_t dv = dim / 4, fv = heads * dim / 4;
+  if (!(dim % 4 == 0 && (dv & (dv - 1)) == 0 && dv <= 32 && fv <= 128 && aligned16(l) && aligned16(r)))
+    return fail(GPHL_ERR_UNSUPPORTED, "u_dot_v (row order) needs 16-byte aligned rows of at most 512 columns and heads of "
+                "4, 8, ..., 128 columns");
+  const int64_t lpr = fv <= 1 ? 1 : fv <= 2 ? 2 : fv <= 4 ? 4 : fv <= 8 ? 8 : fv <= 16 ? 16 : 32;
+  const int64_t nv = fv <= 32 ? 1 : fv <= 64 ? 2 : 4;
+  if (dv % nv != 0 || dv / nv > lpr)
+    return fail(GPHL_ERR_UNSUPPORTED, "u_dot_v (row order): a head of %lld columns does not fit the lane layout", (long long)dim);
+#define GPHL_CSC(L, V) return launch_u_dot_v_csc<L, V>(plan, pointer, idx, eidx, n_rows, heads, fv, dv, l, r, z, stream)
+  switch (lpr) {
+    case 1: GPHL_CSC(1, 1);
+    case 2: GPHL_CSC(2, 1);
+    case 4: GPHL_CSC(4, 1);
+    case 8: GPHL_CSC(8, 1);
+    case 16: GPHL_CSC(16, 1);
+    default:
+      if (nv == 1) GPHL_CSC(32, 1);
+      if (nv == 2) GPHL_CSC(32, 2);
+      GPHL_CSC(32, 4);
+  }
+#undef GPHL_CSC
 }
 
 // ---- attention scores per node and head: el[n,h] = sum_d z[n,h,d] a_src[h,d], er likewise with a_dst ----

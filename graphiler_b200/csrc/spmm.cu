@@ -33,6 +33,7 @@ struct GatherArgs {
   float slope;
   int32_t relu;          // epilogue: max(., 0)
   int32_t exact;         // 1: compensated accumulation (default), 0: plain fp32 adds
+  int32_t stream;        // 1: index loads and output stores carry the evict-first hint
   int32_t wvec;          // per-head arrays (w | el, er, stats) can be read four heads at a time
   int64_t n_long;        // items [0, n_long) are longer than GPHL_SHORT_ITEM positions; -1: unknown (no plan)
   int32_t F, FV, H, DV;  // columns, 16-byte vectors per row, heads, vectors per head
@@ -212,11 +213,12 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   float *wsm = smem_w + (size_t)warp * 32 * a.H;
 
   int next_idx = 0;
-  if (it.begin + lane < it.end) next_idx = __ldg(a.idx + it.begin + lane);
+  if (it.begin + lane < it.end) next_idx = a.stream ? __ldcs(a.idx + it.begin + lane) : __ldg(a.idx + it.begin + lane);
   for (int base = it.begin; base < it.end; base += 32) {
     const int n = min(32, it.end - base);
     const int my_idx = next_idx;
-    if (base + 32 + lane < it.end) next_idx = __ldg(a.idx + base + 32 + lane);   // prefetch the next batch
+    if (base + 32 + lane < it.end)                                               // prefetch the next batch
+      next_idx = a.stream ? __ldcs(a.idx + base + 32 + lane) : __ldg(a.idx + base + 32 + lane);
     if (MODE != COPY) {
       __syncwarp();
       if (lane < n) {
@@ -348,7 +350,8 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
         if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
         if (a.relu) o[k] = fmaxf(o[k], 0.f);
       }
-      VecOf<T>::store(y + (int64_t)cv[v] * VEC, o);
+      if (a.stream) VecOf<T>::store_cs(y + (int64_t)cv[v] * VEC, o);
+      else VecOf<T>::store(y + (int64_t)cv[v] * VEC, o);
     }
   } else {
     float *hi = a.scratch + (int64_t)(2 * it.slot) * a.plane;
@@ -378,8 +381,8 @@ __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int6
   const int64_t item_id = first_item + ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
   if (item_id >= a.n_items) return;
   const Item it = fetch_item(a.items, a.pointer, item_id);
-  const bool cok = l < a.FV;
-  const int cv = cok ? l : 0;
+  const bool cok = (int)blockIdx.y * LPR + l < a.FV;      // blockIdx.y: column slice of LPR vectors (one slice for narrow rows)
+  const int cv = cok ? (int)blockIdx.y * LPR + l : 0;
   const int head = (MODE == COPY) ? 0 : cv / a.DV;
   AccT<EXACT> acc[VP];
 #pragma unroll
@@ -563,12 +566,152 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_sliced_kernel(GatherArg
   }
 }
 
+// ---- whole wide rows, one warp per item, no cross-lane traffic in the loop --------------------------------------
+// Rows of 32 * NV vectors (512 B per NV): lane l holds vectors l, l + 32, ...; the warp walks the item's positions in
+// order, U rows in flight, every lane reading the same index word (one broadcast access) instead of taking it from a
+// neighbour by shuffle.  The indices of the next U positions are fetched while the current rows are summed.
+template <typename T, int NV, int U, int EXACT>
+__global__ void __launch_bounds__(WARPS * 32) gather_sum_wide_kernel(GatherArgs a) {
+  constexpr int VEC = VecOf<T>::N, VP = VEC / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t item_id = (int64_t)blockIdx.x * WARPS + warp;
+  if (item_id >= a.n_items) return;
+  const Item it = fetch_item(a.items, a.pointer, item_id);
+  bool cok[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) cok[v] = v * 32 + lane < a.FV;
+  AccT<EXACT> acc[NV][VP];
+#pragma unroll
+  for (int v = 0; v < NV; ++v)
+#pragma unroll
+    for (int k = 0; k < VP; ++k) {
+      acc[v][k].hi = 0;
+      if constexpr (EXACT) acc[v][k].lo = 0;
+    }
+  const char *xb = static_cast<const char *>(a.x) + (size_t)lane * 16;
+  const uint32_t row_bytes = (uint32_t)a.FV * 16u;
+  const int32_t *ip = a.idx + it.begin;
+  const int cnt = it.end - it.begin;
+  auto load_row = [&](uint4 (&raw)[NV], int src) {
+    const char *row = xb + (uint64_t)(uint32_t)src * row_bytes;
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+      raw[v] = cok[v] ? __ldg(reinterpret_cast<const uint4 *>(row + v * 512)) : make_uint4(0, 0, 0, 0);
+  };
+  auto add_row = [&](const uint4 (&raw)[NV]) {
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      uint64_t val[VP];
+      unpack_pairs<T>(raw[v], val);
+#pragma unroll
+      for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], v * VP + k);
+    }
+  };
+  int i = 0;
+  int s[U];
+  if (U <= cnt) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) s[u] = __ldg(ip + u);
+  }
+#pragma unroll 1
+  for (; i + U <= cnt; i += U) {
+    uint4 raw[U][NV];
+#pragma unroll
+    for (int u = 0; u < U; ++u) load_row(raw[u], s[u]);
+    if (i + 2 * U <= cnt) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) s[u] = __ldg(ip + i + U + u);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) add_row(raw[u]);
+  }
+  if (i < cnt) {                                   // the last cnt % U positions, all in flight together
+    uint4 raw[U][NV];
+#pragma unroll
+    for (int u = 0; u < U - 1; ++u)
+      if (i + u < cnt) load_row(raw[u], __ldg(ip + i + u));
+#pragma unroll
+    for (int u = 0; u < U - 1; ++u)
+      if (i + u < cnt) add_row(raw[u]);
+  }
+
+  if (it.slot < 0) {
+    T *y = static_cast<T *>(a.y) + (int64_t)it.row * a.F;
+    const float scale = a.dst_scale ? __ldg(a.dst_scale + it.row) : 1.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (!cok[v]) continue;
+      float o[VEC];
+#pragma unroll
+      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(v * VP + k), o[2 * k], o[2 * k + 1]);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
+        if (a.relu) o[k] = fmaxf(o[k], 0.f);
+      }
+      VecOf<T>::store(y + (int64_t)(v * 32 + lane) * VEC, o);
+    }
+  } else {
+    float *hi = a.scratch + (int64_t)(2 * it.slot) * a.plane;
+    float *lo = hi + a.plane;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (!cok[v]) continue;
+#pragma unroll
+      for (int k = 0; k < VP; ++k) {
+        float h0, h1, l0, l1;
+        acc[v][k].planes(h0, h1, l0, l1, v * VP + k);
+        const int c = (v * 32 + lane) * VEC + 2 * k;
+        hi[c] = h0, hi[c + 1] = h1, lo[c] = l0, lo[c + 1] = l1;
+      }
+    }
+  }
+}
+
+template <typename T, int NV, int U>
+static int launch_wide_u(const GatherArgs &a, cudaStream_t stream) {
+  const unsigned grid = (unsigned)((a.n_items + WARPS - 1) / WARPS);
+  const int forced = knob("GPHL_ACC", 0);
+  const int kind = !a.exact ? 0 : forced ? forced : 3;
+  if (kind == 0) gather_sum_wide_kernel<T, NV, U, 0><<<grid, WARPS * 32, 0, stream>>>(a);
+  else if (kind == 1) gather_sum_wide_kernel<T, NV, U, 1><<<grid, WARPS * 32, 0, stream>>>(a);
+  else if (kind == 2) gather_sum_wide_kernel<T, NV, U, 2><<<grid, WARPS * 32, 0, stream>>>(a);
+  else gather_sum_wide_kernel<T, NV, U, 3><<<grid, WARPS * 32, 0, stream>>>(a);
+  return launched("gather_sum_wide_kernel");
+}
+
+template <typename T, int NV>
+static int launch_wide(const GatherArgs &a, cudaStream_t stream) {
+  const int u = knob("GPHL_WIDE_U", NV == 1 ? 4 : 2);
+  if (u >= 8 && NV == 1) return launch_wide_u<T, NV, 8>(a, stream);
+  if (u >= 4 && NV <= 2) return launch_wide_u<T, NV, 4>(a, stream);
+  if (u >= 3 && NV <= 2) return launch_wide_u<T, NV, 3>(a, stream);
+  if (u >= 2) return launch_wide_u<T, NV, 2>(a, stream);
+  return launch_wide_u<T, NV, 1>(a, stream);
+}
+
 template <typename T, int LPR>
 static int launch_sliced(const GatherArgs &a, cudaStream_t stream) {
-  dim3 grid((unsigned)((a.n_items + WARPS - 1) / WARPS), (unsigned)((a.FV + LPR - 1) / LPR));
-  if (a.exact) gather_sum_sliced_kernel<T, LPR, 3><<<grid, WARPS * 32, 0, stream>>>(a);
-  else gather_sum_sliced_kernel<T, LPR, 0><<<grid, WARPS * 32, 0, stream>>>(a);
-  return launched("gather_sum_sliced_kernel");
+  // long items: a warp per (item, slice); short items: LPR lanes per (item, slice)
+  const int64_t n_warp = (a.n_long >= 0 && knob("GPHL_SLICE_ROWS", 1)) ? a.n_long : a.n_items;
+  const unsigned slices = (unsigned)((a.FV + LPR - 1) / LPR);
+  if (n_warp > 0) {
+    GatherArgs w = a;
+    w.n_items = n_warp;
+    dim3 grid((unsigned)((n_warp + WARPS - 1) / WARPS), slices);
+    if (a.exact) gather_sum_sliced_kernel<T, LPR, 3><<<grid, WARPS * 32, 0, stream>>>(w);
+    else gather_sum_sliced_kernel<T, LPR, 0><<<grid, WARPS * 32, 0, stream>>>(w);
+    int rc = launched("gather_sum_sliced_kernel");
+    if (rc != GPHL_OK) return rc;
+  }
+  if (n_warp < a.n_items) {
+    const int64_t threads = (a.n_items - n_warp) * LPR;
+    dim3 grid((unsigned)((threads + 255) / 256), slices);
+    if (a.exact) gather_sum_rows_kernel<T, LPR, COPY, 3><<<grid, 256, 0, stream>>>(a, n_warp);
+    else gather_sum_rows_kernel<T, LPR, COPY, 0><<<grid, 256, 0, stream>>>(a, n_warp);
+    return launched("gather_sum_rows_kernel");
+  }
+  return GPHL_OK;
 }
 
 // Slice width (in 16-byte vectors) for the unweighted sum, 0 = one pass over whole rows (the default: on the 62 M-edge,
@@ -699,6 +842,7 @@ static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t
   constexpr int VEC = VecOf<T>::N;
   if (a.n_items == 0 || a.F == 0) return GPHL_OK;
   a.n_long = -1;
+  a.stream = knob("GPHL_STREAM_HINT", 0);
   if (plan) {
     a.items = plan->items;
     a.n_items = plan->n_items;
@@ -719,7 +863,11 @@ static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t
     if (MODE == MUL_E) a.wvec = a.H % 4 == 0 && aligned16(a.w);
     if (MODE == GAT) a.wvec = a.H % 4 == 0 && aligned16(a.el) && aligned16(a.er) && aligned16(a.stats);
     const int slice = (MODE == COPY) ? slice_lanes(a.FV) : 0;
-    if (MODE == COPY && slice > 0) {
+    if (MODE == COPY && a.FV >= 32 && a.FV <= 128 && knob("GPHL_WIDE", 0)) {
+      if (a.FV <= 32) rc = launch_wide<T, 1>(a, stream);
+      else if (a.FV <= 64) rc = launch_wide<T, 2>(a, stream);
+      else rc = launch_wide<T, 4>(a, stream);
+    } else if (MODE == COPY && slice > 0) {
       if (slice >= 32) rc = launch_sliced<T, 32>(a, stream);
       else if (slice >= 16) rc = launch_sliced<T, 16>(a, stream);
       else if (slice >= 8) rc = launch_sliced<T, 8>(a, stream);

@@ -9,6 +9,7 @@
 // src/ops/segment_softmax/segment_softmax.cu:27-30, src/ops/segment_mm/segment_mm.cu:35-42,
 // src/ops/dgl_primitives/spmm.cu:391-406, src/ops/dgl_primitives/sddmm.cu:131-134.
 // `int? t` is bound as optional<int64_t>: current PyTorch rejects optional<ScalarType> for it.
+#include <cstdlib>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/custom_class.h>
@@ -73,16 +74,59 @@ struct DGLGraph : torch::CustomClassHolder {
                     out_edge_indices.size(0) == num_edges && COO_src.size(0) == num_edges &&
                     COO_dst.size(0) == num_edges,
                 "edge arrays must all have num_edges entries");
+    prepare();
+  }
+  // Everything that needs a host round trip happens here, once per graph, so that no operator call synchronises
+  // or allocates outside PyTorch's caching allocator: the index arrays are validated (the kernels trust them; set
+  // GPHL_SKIP_VALIDATION=1 to skip the pass) and the row-split plans of both sides are built.  Their scratch is
+  // bound per call from the caching allocator (plan()).  CPU tensors are left alone: every operator rejects them.
+  void prepare() {
+    if (!in_pointer.is_cuda() || num_nodes >= INT32_MAX || num_edges >= INT32_MAX) return;
+    c10::cuda::CUDAGuard guard(in_pointer.device());
+    Tensor ip = cuda_idx(in_pointer, torch::kInt32, "in_pointer"), op = cuda_idx(out_pointer, torch::kInt32, "out_pointer");
+    const char *skip = std::getenv("GPHL_SKIP_VALIDATION");
+    if (!(skip && skip[0] == '1')) {
+      Tensor inn = cuda_idx(in_node_indices, torch::kInt32, "in_node_indices");
+      Tensor ine = cuda_idx(in_edge_indices, torch::kInt32, "in_edge_indices");
+      Tensor outn = cuda_idx(out_node_indices, torch::kInt32, "out_node_indices");
+      Tensor oute = cuda_idx(out_edge_indices, torch::kInt32, "out_edge_indices");
+      Tensor cs = cuda_idx(COO_src, torch::kInt64, "COO_src"), cd = cuda_idx(COO_dst, torch::kInt64, "COO_dst");
+      void *st = stream_of(ip);
+      check_rc(gphl_validate_csr(ip.data_ptr<int32_t>(), num_nodes, num_edges, ptr_or<int32_t>(inn, ip), num_nodes,
+                                 ptr_or<int32_t>(ine, ip), num_edges, st), "DGLGraph: in-edge arrays");
+      check_rc(gphl_validate_csr(op.data_ptr<int32_t>(), num_nodes, num_edges, ptr_or<int32_t>(outn, op), num_nodes,
+                                 ptr_or<int32_t>(oute, op), num_edges, st), "DGLGraph: out-edge arrays");
+      check_rc(gphl_validate_index_i64(num_edges ? cs.data_ptr<int64_t>() : nullptr, num_edges, num_nodes, st), "DGLGraph: COO_src");
+      check_rc(gphl_validate_index_i64(num_edges ? cd.data_ptr<int64_t>() : nullptr, num_edges, num_nodes, st), "DGLGraph: COO_dst");
+      if (ntype_pointer.has_value()) check_type_pointer(ntype_pointer.value(), num_nodes, "ntype_pointer");
+      if (etype_pointer.has_value()) check_type_pointer(etype_pointer.value(), num_edges, "etype_pointer");
+    }
+    check_rc(gphl_plan_create(ip.data_ptr<int32_t>(), num_nodes, GPHL_DEFAULT_CHUNK, 0, stream_of(ip), &plan_in), "gphl_plan_create");
+    check_rc(gphl_plan_create(op.data_ptr<int32_t>(), num_nodes, GPHL_DEFAULT_CHUNK, 0, stream_of(op), &plan_out), "gphl_plan_create");
+  }
+  // A type pointer must be non-decreasing from 0 to the number of rows it partitions: the typed-linear kernels write
+  // exactly the rows it covers (the reference's loop of at::mm + cat, segment_mm.cu:4-21, would return a shorter
+  // tensor or raise for anything else).
+  static void check_type_pointer(const Tensor &pointer, int64_t rows, const char *what) {
+    if (!pointer.is_cuda()) return;
+    const char *skip = std::getenv("GPHL_SKIP_VALIDATION");
+    if (skip && skip[0] == '1') return;
+    Tensor pc = cuda_idx(pointer, torch::kInt32, what);
+    TORCH_CHECK(pc.numel() >= 1, what, " must have at least one entry");
+    c10::cuda::CUDAGuard guard(pc.device());
+    check_rc(gphl_validate_csr(pc.data_ptr<int32_t>(), pc.numel() - 1, rows, nullptr, 0, nullptr, 0, stream_of(pc)), what);
   }
   ~DGLGraph() override {
     gphl_plan_destroy(plan_in);
     gphl_plan_destroy(plan_out);
   }
   void SetNtypePointer(Tensor pointer) {
+    check_type_pointer(pointer, num_nodes, "ntype_pointer");
     ntype_pointer = pointer;
     num_ntypes = pointer.size(0) - 1;
   }
   void SetEtypePointer(Tensor pointer) {
+    check_type_pointer(pointer, num_edges, "etype_pointer");
     etype_pointer = pointer;
     num_etypes = pointer.size(0) - 1;
   }
@@ -95,21 +139,20 @@ struct DGLGraph : torch::CustomClassHolder {
     etype_COO = t;
   }
 
-  // Plan for the reduce side (rows = destinations) or the message side (rows = sources), built
-  // on first use (one device-to-host copy of the pointer array per graph) and rebuilt only if a
-  // wider feature needs more scratch.
+  // Plan for the reduce side (rows = destinations) or the message side (rows = sources).  The plans were built in the
+  // constructor; here only the scratch of the cut rows is bound, from PyTorch's caching allocator (no cudaMalloc,
+  // no synchronisation), kept per graph and grown when a wider feature arrives.  Calls on one graph from several
+  // streams at once would share it, as they would share any per-graph state.
   const gphl_plan *plan(bool reduce_side, int64_t feat) {
     gphl_plan *&p = reduce_side ? plan_in : plan_out;
+    TORCH_CHECK(p != nullptr, "DGLGraph was built from CPU tensors: this library has no CPU path");
     int64_t &width = reduce_side ? plan_in_width : plan_out_width;
-    if (p == nullptr || feat > width) {
-      gphl_plan_destroy(p);
-      p = nullptr;
-      const Tensor &ptr = reduce_side ? in_pointer : out_pointer;
-      Tensor pc = cuda_idx(ptr, torch::kInt32, "pointer");
-      width = std::max<int64_t>(feat, 256);
-      c10::cuda::CUDAGuard guard(pc.device());
-      check_rc(gphl_plan_create(pc.data_ptr<int32_t>(), num_nodes, GPHL_DEFAULT_CHUNK, width, stream_of(pc), &p),
-               "gphl_plan_create");
+    Tensor &scratch = reduce_side ? scratch_in : scratch_out;
+    if (feat > width) {
+      const int64_t pieces = gphl_plan_num_pieces(p);
+      width = std::max<int64_t>((feat + 7) / 8 * 8, 256);
+      if (pieces > 0) scratch = torch::empty({2 * pieces * width}, in_pointer.options().dtype(torch::kFloat32));
+      check_rc(gphl_plan_bind_scratch(p, pieces > 0 ? scratch.data_ptr() : nullptr, width), "gphl_plan_bind_scratch");
     }
     return p;
   }
@@ -126,7 +169,7 @@ struct DGLGraph : torch::CustomClassHolder {
   }
 
   int64_t num_nodes, num_edges, num_ntypes, num_etypes;
-  Tensor edge_pos32, dst32;
+  Tensor edge_pos32, dst32, scratch_in, scratch_out;
   Tensor in_pointer, in_node_indices, in_edge_indices;
   Tensor out_pointer, out_node_indices, out_edge_indices;
   Tensor COO_src, COO_dst;
@@ -265,6 +308,19 @@ Tensor SpMMEdgeMul(Tensor a, Tensor b, const GraphPtr &g) {
 }
 
 // ---- SDDMM --------------------------------------------------------------------------------
+// Shapes the destination-row dot-product kernel covers (gphl_sddmm_u_dot_v_csc_f32): heads of 4, 8, ..., 128 columns
+// that fit the lane layout, rows of at most 512 columns.  torch allocations are 16-byte aligned.
+static bool csc_dot_fits(int64_t f, int64_t heads) {
+  if (heads < 1 || f % heads != 0) return false;
+  const int64_t dim = f / heads;
+  if (dim % 4 != 0) return false;
+  const int64_t dv = dim / 4, fv = f / 4;
+  if ((dv & (dv - 1)) != 0 || dv > 32 || fv > 128) return false;
+  const int64_t lpr = fv <= 1 ? 1 : fv <= 2 ? 2 : fv <= 4 ? 4 : fv <= 8 ? 8 : fv <= 16 ? 16 : 32;
+  const int64_t nv = fv <= 32 ? 1 : fv <= 64 ? 2 : 4;
+  return dv % nv == 0 && dv / nv <= lpr;
+}
+
 Tensor u_add_v_mul_alpha(Tensor l, Tensor r, int64_t /*alpha: ignored, as in the reference*/, const GraphPtr &g) {
   Tensor lc = cuda_f32(l, "source features"), rc_ = cuda_f32(r, "destination features");
   const int64_t f = feat_of(lc);
@@ -294,8 +350,19 @@ Tensor u_dot_v(Tensor l, Tensor r, int64_t heads, const GraphPtr &g) {
   Tensor lc = l.contiguous(), rc_ = r.contiguous();
   const int64_t f = lc.size(1);
   Tensor z = torch::empty({g->num_edges, heads}, lc.options());
-  Tensor s = cuda_idx(g->COO_src, torch::kInt64, "COO_src"), d = cuda_idx(g->COO_dst, torch::kInt64, "COO_dst");
+  if (g->num_edges == 0) return z;
   c10::cuda::CUDAGuard guard(lc.device());
+  if (csc_dot_fits(f, heads)) {          // destination-row order: r[v] once per row, half the gathered bytes
+    Tensor ptr = cuda_idx(g->in_pointer, torch::kInt32, "in_pointer");
+    Tensor nid = cuda_idx(g->in_node_indices, torch::kInt32, "in_node_indices");
+    Tensor eid = cuda_idx(g->in_edge_indices, torch::kInt32, "in_edge_indices");
+    check_rc(gphl_sddmm_u_dot_v_csc_f32(g->plan(true, f), ptr.data_ptr<int32_t>(), nid.data_ptr<int32_t>(),
+                                        eid.data_ptr<int32_t>(), g->num_nodes, heads, f / heads, lc.data_ptr<float>(),
+                                        rc_.data_ptr<float>(), z.data_ptr<float>(), stream_of(lc)),
+             "gphl_sddmm_u_dot_v_csc_f32");
+    return z;
+  }
+  Tensor s = cuda_idx(g->COO_src, torch::kInt64, "COO_src"), d = cuda_idx(g->COO_dst, torch::kInt64, "COO_dst");
   check_rc(gphl_sddmm_u_dot_v_f32_i64(s.data_ptr<int64_t>(), d.data_ptr<int64_t>(), g->num_edges, heads, f / heads,
                                       lc.data_ptr<float>(), rc_.data_ptr<float>(), z.data_ptr<float>(), stream_of(lc)),
            "gphl_sddmm_u_dot_v_f32_i64");
@@ -318,6 +385,15 @@ Tensor e_dot_v(Tensor e, Tensor v, int64_t heads, const GraphPtr &g) {
   Tensor z = torch::empty({g->num_edges, heads}, ec.options());
   if (g->num_edges == 0) return z;
   c10::cuda::CUDAGuard guard(ec.device());
+  if (csc_dot_fits(f, heads)) {          // rows of e are addressed by edge id, v[dst] is read once per destination row
+    Tensor ptr = cuda_idx(g->in_pointer, torch::kInt32, "in_pointer");
+    Tensor eid = cuda_idx(g->in_edge_indices, torch::kInt32, "in_edge_indices");
+    check_rc(gphl_sddmm_u_dot_v_csc_f32(g->plan(true, f), ptr.data_ptr<int32_t>(), eid.data_ptr<int32_t>(),
+                                        eid.data_ptr<int32_t>(), g->num_nodes, heads, f / heads, ec.data_ptr<float>(),
+                                        vc.data_ptr<float>(), z.data_ptr<float>(), stream_of(ec)),
+             "gphl_sddmm_u_dot_v_csc_f32");
+    return z;
+  }
   const Tensor &pos = g->edge_positions32(), &dst = g->coo_dst32();
   check_rc(gphl_sddmm_u_dot_v_f32_i32(pos.data_ptr<int32_t>(), dst.data_ptr<int32_t>(), g->num_edges, heads, f / heads,
                                       ec.data_ptr<float>(), vc.data_ptr<float>(), z.data_ptr<float>(), stream_of(ec)),

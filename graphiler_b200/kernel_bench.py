@@ -24,7 +24,7 @@ import torch
 
 from . import capi, layers, synthetic
 
-KERNELS = ("linear", "copy_u_sum", "copy_e_sum", "u_mul_e_sum", "u_add_v", "u_dot_v", "segment_softmax", "gat_fused",
+KERNELS = ("linear", "copy_u_sum", "copy_e_sum", "u_mul_e_sum", "u_add_v", "u_dot_v", "u_dot_v_csc", "segment_softmax", "gat_fused",
            "broadcast_src", "segment_mm_node", "segment_mm_edge")
 
 
@@ -72,6 +72,12 @@ def run(config: str, kernel: str, scale: float, iters: int, warmup: int, feat: i
         r = torch.randn(n, feat, generator=gen, device=device)
         fn = lambda: capi.sddmm_u_dot_v(pg.COO_src32, pg.COO_dst32, x, r, heads)
         b_alg = 2 * e * 4 + 2 * n * feat * 4 + e * heads * 4
+    elif kernel == "u_dot_v_csc":               # the same dot products walked in destination-row order
+        r = torch.randn(n, feat, generator=gen, device=device)
+        plan = pg.plan_in(feat)
+        z = torch.empty(e, heads, device=device)
+        fn = lambda: capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_node_indices, g.in_edge_indices, x, r, heads, plan, out=z)
+        b_alg = (n + 1) * 4 + 2 * e * 4 + 2 * n * feat * 4 + e * heads * 4
     elif kernel == "segment_softmax":
         lg = torch.randn(e, heads, generator=gen, device=device)
         plan = pg.plan_in(feat)

@@ -118,7 +118,8 @@ def hgt_layer(pg: PreparedGraph, h, p: Dict[str, torch.Tensor], heads: int, sqrt
     q = capi.segment_mm(h, p["q_weight"], g.ntype_pointer)
     k2 = capi.segment_mm(k, p["relation_att"], g.etype_pointer, gather_idx=g.COO_src)
     v2 = capi.segment_mm(v, p["relation_msg"], g.etype_pointer, gather_idx=g.COO_src)
-    s = capi.sddmm_u_dot_v(pg._arange_e, pg.COO_dst32, k2, q, heads)               # k2 is already edge-level
+    # k2 is already edge-level: walk the destination rows, q[v] read once per row, k2 rows addressed by edge id
+    s = capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_edge_indices, g.in_edge_indices, k2, q, heads, pg.plan_in(k2.shape[1]))
     pri = capi.gather_rows(g.etype_COO, p["relation_pri"])
     s = s.mul_(pri).div_(sqrt_dk)
     plan = pg.plan_in(v2.shape[1])

@@ -58,6 +58,21 @@ void gphl_plan_destroy(gphl_plan *plan);
 int64_t gphl_plan_num_items(const gphl_plan *plan);      /* work items (rows + extra pieces)   */
 int64_t gphl_plan_num_split_rows(const gphl_plan *plan); /* rows that were cut                 */
 int64_t gphl_plan_scratch_bytes(const gphl_plan *plan);
+int64_t gphl_plan_num_pieces(const gphl_plan *plan);     /* pieces of cut rows = scratch slots */
+/* A plan created with max_feat = 0 owns no scratch.  A caller with its own allocator (the TorchScript shims use
+ * PyTorch's caching allocator, so that no operator call reaches cudaMalloc) binds a 16-byte aligned buffer of
+ * 2 * num_pieces * round_up(max_feat, 8) floats before calls whose feature width is at most max_feat.  The plan
+ * does not own a bound buffer.  Not to be called while another thread uses the plan. */
+int gphl_plan_bind_scratch(gphl_plan *plan, void *scratch, int64_t max_feat);
+
+/* ---- validation of graph arrays (no counterpart in the reference, which checks nothing: src/dglgraph.cpp:5-24) ------
+ * The kernels trust their index arrays.  These check them once, where a graph enters the library: the pointer array
+ * is non-decreasing, starts at 0 and ends at n_entries; every idx value lies in [0, idx_limit) and every eidx value
+ * (optional) in [0, eidx_limit).  One pass over the arrays on `stream`, which is synchronised; returns GPHL_OK or
+ * GPHL_ERR_INVALID_ARGUMENT with gphl_last_error() naming the violation. */
+int gphl_validate_csr(const int32_t *pointer, int64_t n_rows, int64_t n_entries, const int32_t *idx, int64_t idx_limit,
+                      const int32_t *eidx, int64_t eidx_limit, void *stream);
+int gphl_validate_index_i64(const int64_t *index, int64_t n, int64_t limit, void *stream);
 
 /* ---- SpMM: y[v,:] = sum_{i in seg(v)} x[idx[i],:] ------------------------------------
  * copy_u_sum when idx = in_node_indices (my_ops::SpMMSrc, spmm.cu:375-389) and copy_e_sum
@@ -108,6 +123,14 @@ int gphl_sddmm_u_dot_v_f32_i64(const int64_t *src, const int64_t *dst, int64_t n
                                int64_t dim, const float *l, const float *r, float *z, void *stream);
 int gphl_sddmm_u_dot_v_f32_i32(const int32_t *src, const int32_t *dst, int64_t n_edges, int64_t heads,
                                int64_t dim, const float *l, const float *r, float *z, void *stream);
+/* The same dot products walked in destination-row order over the CSC arrays (the reference's SDDMM has a CSR
+ * variant beside the COO one, sddmm.cuh:150-199 SDDMMCsrKernel): for every position i of row v,
+ * z[eid[i],h] = sum_d l[idx[i],h,d] * r[v,h,d]; r[v] is read once per row, not once per edge.  `eidx` NULL means
+ * edge id == position.  `plan` (optional) is the row-split plan of `pointer`.  Heads of 4, 8, ..., 128 columns, rows
+ * of at most 512 columns, 16-byte aligned; other shapes return GPHL_ERR_UNSUPPORTED (use the COO form). */
+int gphl_sddmm_u_dot_v_csc_f32(const gphl_plan *plan, const int32_t *pointer, const int32_t *idx, const int32_t *eidx,
+                               int64_t n_rows, int64_t heads, int64_t dim, const float *l, const float *r, float *z,
+                               void *stream);
 
 /* ---- segment softmax: per row v and head h, softmax over x[edge_idx[seg(v)],h] ---------
  * my_ops::SegmentSoftmax (segment_softmax.cu:3-24; kernel softmax_v,

@@ -17,7 +17,7 @@ def declared_functions():
 def test_header_declares_the_operator_set():
     names = declared_functions()
     for must in ("gphl_spmm_gather_sum_f32", "gphl_spmm_u_mul_e_sum_f32", "gphl_sddmm_u_add_v_f32_i64",
-                 "gphl_sddmm_u_dot_v_f32_i64", "gphl_segment_softmax_f32", "gphl_gat_fused_f32",
+                 "gphl_sddmm_u_dot_v_f32_i64", "gphl_sddmm_u_dot_v_csc_f32", "gphl_segment_softmax_f32", "gphl_gat_fused_f32",
                  "gphl_gather_rows_i64", "gphl_segment_mm_f32", "gphl_plan_create"):
         assert must in names
 

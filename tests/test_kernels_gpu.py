@@ -187,6 +187,32 @@ def test_sddmm_u_dot_v(graph, heads, dim):
     assert torch.equal(z, z32)
 
 
+@pytest.mark.parametrize("heads,dim", [(8, 16), (1, 64), (8, 32), (4, 128), (2, 64), (64, 4), (32, 8), (16, 16), (1, 4), (2, 4),
+                                       (1, 8), (4, 4), (1, 128), (8, 64)])
+@pytest.mark.parametrize("with_plan", [False, True])
+def test_sddmm_u_dot_v_row_order(graph, heads, dim, with_plan):
+    """The destination-row (CSC) walk returns the COO result for every edge: node-level operands gathered by source
+    id, and edge-level left operands addressed by edge id (the HGT form), with and without the row-split plan."""
+    g = graph.to(DEV)
+    f = heads * dim
+    l = torch.randn(g.num_nodes, f, device=DEV)
+    r = torch.randn(g.num_nodes, f, device=DEV)
+    plan = capi.Plan(g.in_pointer, f, chunk=8) if with_plan else None          # chunk 8: rows cut into pieces
+    z = capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_node_indices, g.in_edge_indices, l, r, heads, plan)
+    close(z, O.sddmm_u_dot_v(l, r, graph.COO_src, graph.COO_dst, heads))
+    le = torch.randn(g.num_edges, f, device=DEV)
+    z = capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_edge_indices, g.in_edge_indices, le, r, heads, plan)
+    truth = O.sddmm_u_dot_v(le, r, torch.arange(graph.num_edges), graph.COO_dst, heads)
+    close(z, truth)
+
+
+def test_sddmm_u_dot_v_row_order_refuses_other_shapes(graph):
+    g = graph.to(DEV)
+    l = torch.randn(g.num_nodes, 15, device=DEV)
+    with pytest.raises(capi.GphlError):
+        capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_node_indices, g.in_edge_indices, l, l, 3)
+
+
 @pytest.mark.parametrize("heads", [1, 8, 3, 40])
 @pytest.mark.parametrize("use_plan", [False, True])
 def test_segment_softmax(graph, heads, use_plan):

@@ -180,3 +180,38 @@ def test_synthetic_generators_are_seeded_and_valid():
     assert bool((c3.graph.etype_COO[1:] >= c3.graph.etype_COO[:-1]).all())      # edges sorted by relation
     c1 = synthetic.make_c1(scale=0.01)
     assert torch.equal(c1.graph.in_edge_indices, torch.arange(c1.graph.num_edges, dtype=torch.int32))
+
+
+def test_c_restatement_matches_numpy_oracle():
+    """oracle/csr_cpu.c (the compiled checker for the full-size cases and the timed CPU baseline) against the numpy
+    oracle, which is itself pinned on the reference operators' recorded outputs."""
+    from oracle import csr_cpu as K
+    from fixtures_common import hetero_graphs
+    g = random_graph(300, 4000, 5)
+    rng = np.random.default_rng(5)
+    n, e = g.num_nodes, g.num_edges
+    x = rng.standard_normal((n, 24)).astype(np.float32)
+    sc = rng.random(n).astype(np.float32)
+    t = O.spmm_src(x, g.in_pointer, g.in_node_indices)
+    assert np.allclose(K.gather_sum_f64(g.in_pointer, g.in_node_indices, x), t, rtol=1e-13, atol=1e-13)
+    part = K.gather_sum_f64(g.in_pointer, g.in_node_indices, x, dst_scale=sc, relu=True, rows=(17, 211))
+    assert np.allclose(part, np.maximum(t * sc[:, None].astype(np.float64), 0)[17:211], rtol=1e-13, atol=1e-13)
+    f32 = K.gather_sum_f32(g.in_pointer, g.in_node_indices, x)
+    assert O.within_tolerance(f32, t, rtol=1e-4, atol=1e-5)[0]
+    w = rng.standard_normal((e, 4)).astype(np.float32)
+    t = O.u_mul_e_sum(x, w, g.in_pointer, g.in_node_indices, g.in_edge_indices)
+    assert np.allclose(K.u_mul_e_sum_f64(g.in_pointer, g.in_node_indices, g.in_edge_indices, x, w), t, rtol=1e-12, atol=1e-12)
+    z = (3 * rng.standard_normal((e, 4))).astype(np.float32)
+    t = O.segment_softmax(z, g.in_pointer, g.in_edge_indices)
+    assert np.allclose(K.segment_softmax_f64(g.in_pointer, g.in_edge_indices, z), t, rtol=1e-12, atol=1e-15)
+    r = rng.standard_normal((n, 24)).astype(np.float32)
+    t = O.sddmm_u_dot_v(x, r, g.COO_src, g.COO_dst, 4)
+    assert np.allclose(K.u_dot_v_f64(g.COO_src, g.COO_dst, x, r, 4), t, rtol=1e-12, atol=1e-12)
+    hg = hetero_graphs()["rand_hetero"]
+    xe = rng.standard_normal((hg.num_edges, 12)).astype(np.float32)
+    we = rng.standard_normal((hg.num_etypes, 12, 20)).astype(np.float32)
+    t = O.segment_mm(xe, we, hg.etype_pointer)
+    assert np.allclose(K.segment_mm_f64(xe, we, hg.etype_pointer), t, rtol=1e-12, atol=1e-12)
+    xn = rng.standard_normal((hg.num_nodes, 12)).astype(np.float32)
+    t = O.segment_mm(xn[hg.COO_src.numpy()], we, hg.etype_pointer)
+    assert np.allclose(K.segment_mm_f64(xn, we, hg.etype_pointer, gather=hg.COO_src), t, rtol=1e-12, atol=1e-12)

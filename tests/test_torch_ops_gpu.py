@@ -117,3 +117,76 @@ def test_prepare_graph_on_device_matches_host():
     for name in ("in_pointer", "in_node_indices", "in_edge_indices", "out_pointer", "out_node_indices",
                  "out_edge_indices", "COO_src", "COO_dst"):
         assert torch.equal(getattr(gd, name).cpu(), getattr(g, name)), name
+
+
+def _ctor(d, **over):
+    a = {k: getattr(d, k) for k in ("in_pointer", "in_node_indices", "in_edge_indices", "out_pointer", "out_node_indices",
+                                    "out_edge_indices", "COO_src", "COO_dst")}
+    a.update(over)
+    return torch.classes.my_classes.DGLGraph(a["in_pointer"], a["in_node_indices"], a["in_edge_indices"], a["out_pointer"],
+                                             a["out_node_indices"], a["out_edge_indices"], a["COO_src"], a["COO_dst"],
+                                             None, None)
+
+
+def test_graph_arrays_are_validated_at_construction(ops):
+    """An index out of range, a pointer array that decreases or does not end at the edge count, and a type pointer
+    that does not cover its rows are refused with an error where the graph enters the library, not read out of
+    bounds by a kernel later.  The context stays usable."""
+    d = typed_random_graph().to(DEV)
+    n, e = d.num_nodes, d.num_edges
+    bad = d.in_node_indices.clone()
+    bad[7] = n                                                  # one past the last node
+    with pytest.raises(RuntimeError, match="neighbour index"):
+        _ctor(d, in_node_indices=bad)
+    bad = d.out_edge_indices.clone()
+    bad[0] = -1
+    with pytest.raises(RuntimeError, match="edge index"):
+        _ctor(d, out_edge_indices=bad)
+    bad = d.in_pointer.clone()
+    bad[5], bad[6] = bad[6].item() + 1, bad[5].item()
+    with pytest.raises(RuntimeError, match="pointer array"):
+        _ctor(d, in_pointer=bad)
+    bad = d.in_pointer.clone()
+    bad[-1] = e - 1
+    with pytest.raises(RuntimeError, match="pointer array"):
+        _ctor(d, in_pointer=bad)
+    bad = d.COO_dst.clone()
+    bad[3] = n + 5
+    with pytest.raises(RuntimeError, match="COO_dst"):
+        _ctor(d, COO_dst=bad)
+    G = _ctor(d)
+    short = d.etype_pointer.clone()
+    short[-1] = e - 3                                           # leaves three edges without a type
+    with pytest.raises(RuntimeError, match="etype_pointer"):
+        G.SetEtypePointer(short)
+    G.SetEtypePointer(d.etype_pointer)
+    y = ops.SpMMSrc(torch.ones(n, 4, device=DEV), [1], False, None, G)
+    assert torch.equal(y.cpu()[:, 0], typed_random_graph().in_degrees().float())
+
+
+def test_first_operator_call_on_a_graph_can_be_captured(ops):
+    """No operator call synchronises or allocates device memory behind PyTorch's allocator: the very first calls on a
+    freshly built graph (rows cut into pieces, so scratch is needed) run inside a CUDA-graph capture, which refuses
+    both, and the replay gives the eager result."""
+    from graphiler_b200 import synthetic
+    wl = synthetic.make_c5(scale=0.002)
+    d = wl.graph.to(DEV)
+    assert int(d.in_degrees().max()) > 512                      # at least one row is cut
+    x = torch.randn(d.num_nodes, 64, device=DEV)
+    w = torch.rand(d.num_edges, 1, device=DEV)
+    G = _ctor(d)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            y = ops.SpMMSrc(x, [1], False, None, G)
+            a = ops.SegmentSoftmax(w, 1, None, G)
+            z = ops.gspmm_src_mul_e_sum(x, a, [1], False, None, G)
+    graph.replay()
+    torch.cuda.synchronize()
+    G2 = _ctor(d)
+    assert torch.equal(y, ops.SpMMSrc(x, [1], False, None, G2))
+    assert torch.equal(z, ops.gspmm_src_mul_e_sum(x, ops.SegmentSoftmax(w, 1, None, G2), [1], False, None, G2))
+    close(y, O.spmm_src(x, wl.graph.in_pointer, wl.graph.in_node_indices))
