@@ -219,8 +219,11 @@ def workload_config(g, args, world):
             "nodes": g.num_nodes, "edges_incl_self_loops": g.num_edges, "feat": 256, "scale": args.scale,
             "storage": args.dtype, "accumulation": "fp32 plain" if getattr(args, "fast_accum", False) else "fp32 compensated (two-sum)",
             "partition": ("none" if world == 1 else f"dst-rows x{world} (edge-balanced) + all-gather in {args.gather_chunks} overlapped pieces"
-                          if args.exchange == "allgather" else f"dst-rows x{world} (edge-balanced) + halo all-to-all of the rows each shard reads, source rows "
-                          + ("dealt to the ranks by a hash of their id" if args.ownership != "blocks" else "owned in contiguous blocks")),
+                          if args.exchange == "allgather" else f"dst-rows x{world} (edge-balanced) + "
+                          + ("halo all-to-all of the rows each shard reads" if args.exchange == "halo" else
+                             "the rows each shard reads stored into its peer-mapped buffer by the senders' row-gather kernel over NVLink")
+                          + ", source rows " + ("dealt to the ranks by a hash of their id" if args.ownership != "blocks" else "owned in contiguous blocks")
+                          + (f" (peer stores unavailable: {args.push_unavailable})" if getattr(args, "push_unavailable", None) else "")),
             "l2": "inputs (2.4 GB features, 0.25 GB indices) exceed the 126 MB L2; no flush between steps"}
 
 
@@ -306,6 +309,9 @@ def extras_per_config(dev):
     p, hy, g = w.params, w.hyper, w.graph
     n, e, H = g.num_nodes, g.num_edges, int(hy["heads"])
     ms_gat = t(lambda: layers.gat_layer(pg, w.feats, p["fc_weight"], p["attn_src"], p["attn_dst"], hy["slope"]), iters=10, warm=3)
+    y_gat = layers.gat_layer(pg, w.feats, p["fc_weight"], p["attn_src"], p["attn_dst"], hy["slope"])
+    gat_checksum = f"{int(y_gat.view(torch.int32).to(torch.int64).sum().item()) & 0xFFFFFFFFFFFFFFFF:016x}"
+    del y_gat
     z, el, er = layers.gat_projections(w.feats, p["fc_weight"], p["attn_src"], p["attn_dst"])
     plan = pg.plan_in(256)
     st = torch.empty(2 * n * H, device=dev)
@@ -317,7 +323,7 @@ def extras_per_config(dev):
     out["c5_gat"] = {"layer_ms": ms_gat, "gat_fused_ms": ms_k, "gat_fused_gbs": b_alg / ms_k / 1e6,
                      "gat_fused_frac": b_alg / ms_k / 1e6 / hbm, "gat_fused_bf16_ms": ms_kb,
                      "copy_u_sum_bf16_ms": ms_sb, "copy_u_sum_bf16_gbs": ((n + 1) * 4 + e * 4 + 2 * n * 256 * 2) / ms_sb / 1e6,
-                     "nodes": n, "edges": e}
+                     "nodes": n, "edges": e, "output_checksum": gat_checksum}
     del w, pg, z, el, er, zb, st, plan
     torch.cuda.empty_cache()
     # c1 GAT
@@ -416,7 +422,10 @@ def run_native(args):
 
     sl = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, feat, dtype=dtype, rank=rank, world=world,
                             chunks=args.gather_chunks, exchange=args.exchange,
-                            ownership=(args.ownership if args.exchange == "halo" and args.ownership != "auto" else None))
+                            ownership=(args.ownership if args.exchange in ("halo", "push") and args.ownership != "auto" else None))
+    if args.exchange == "push" and world > 1 and not sl.push:
+        args.exchange = "halo"                       # symmetric memory unavailable: the all-to-all took over
+        args.push_unavailable = sl.push_unavailable
     own = sl.owned_rows                              # source rows this rank projects (a block, or dealt by hash)
     r0, r1 = sl.shard.row0, sl.shard.row1
     x_blk, nsrc_blk, ndst_loc = x[own].contiguous(), norm[own].contiguous(), norm[r0:r1].contiguous()
@@ -455,7 +464,7 @@ def run_native(args):
         step()
     sync()
     kev.clear()
-    if world > 1 and args.exchange == "halo":
+    if world > 1 and args.exchange in ("halo", "push"):
         sl.phase_marks = []
     sampler = ClockSampler(local)
     if rank == 0:
@@ -613,6 +622,38 @@ def run_native(args):
                                 "udf_path": cpu.udf_slice(args.cpu_fraction),
                                 "reference_gpu_ops_ms": reference_gpu_ops(args.scale)}
         del cpu
+    if world > 1 and not args.no_extras:
+        # the other scale-sweep variants at this GPU count: bf16 storage of the same GCN layer, and the GAT layer
+        # (8 heads x 32; z, el, er all-gathered, fused attention on the local destination rows)
+        extras = {}
+        del sl, out
+        torch.cuda.empty_cache()
+        slb = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, feat, dtype=torch.bfloat16, rank=rank, world=world,
+                                 chunks=args.gather_chunks, exchange=args.exchange)
+        xb, nsb = x_blk, norm[slb.owned_rows].contiguous()      # the same rows: ownership depends on the exchange only
+        ndb = norm[slb.shard.row0:slb.shard.row1].contiguous()
+        fb = lambda: gdist.gcn_layer_sharded(slb, xb, w, nsb, ndb)
+        tb = torch.tensor([time_loop(fb, max(3, args.steps // 2), 3, sync)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+        extras["c5_gcn_bf16_storage"] = {"layer_ms": float(tb[0]), "exchange": "peer stores" if slb.push else slb.exchange}
+        del slb
+        torch.cuda.empty_cache()
+        wl2 = synthetic.make_c5(scale=args.scale, device=dev)
+        p2, hy = wl2.params, wl2.hyper
+        slg = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, p2["fc_weight"].shape[1], rank=rank, world=world)
+        lo, hi = slg.block_range
+        xg = wl2.feats[lo:hi].contiguous()
+        del wl2
+        fg = lambda: gdist.gat_layer_sharded(slg, xg, p2["fc_weight"], p2["attn_src"], p2["attn_dst"], hy["slope"])
+        tg = torch.tensor([time_loop(fg, max(3, args.steps // 2), 3, sync)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        yg = fg()
+        cg = yg.view(torch.int32).to(torch.int64).sum().reshape(1)
+        dist.all_reduce(cg, op=dist.ReduceOp.SUM)
+        extras["c5_gat"] = {"layer_ms": float(tg[0]), "exchange": "allgather of z, el, er",
+                            "output_checksum": f"{int(cg.item()) & 0xFFFFFFFFFFFFFFFF:016x}"}
+        if rank == 0:
+            line["per_config"] = extras
     if rank == 0 and world == 1 and not args.no_extras:
         del sl, out, x_blk
         torch.cuda.empty_cache()
@@ -639,9 +680,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--ownership", default="auto", choices=["auto", "blocks", "hashed"],
                     help="halo exchange: which rank projects which source rows (auto = hashed)")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "halo"],
-                    help="N > 1: all-gather every projected row, or send each shard only the rows it reads (all-to-all); "
-                         "auto = halo from 4 GPUs up (measured: 3.9 vs 5.1 ms at 8, 5.4 vs 5.5 at 4, 7.9 vs 6.8 at 2)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "halo", "push"],
+                    help="N > 1: all-gather every projected row; halo = send each shard only the rows it reads (all-to-all); "
+                         "push = the same rows stored straight into the receivers' peer-mapped buffers by the row-gather "
+                         "kernel (falls back to halo where symmetric memory is unavailable); auto = push from 4 GPUs up")
     ap.add_argument("--gather-chunks", type=int, default=4,
                     help="N > 1: pieces the projection + all-gather is cut into so that they overlap")
     ap.add_argument("--cublas-projection", action="store_true",
@@ -652,7 +694,7 @@ def main():
                     help="plain fp32 accumulation in the SpMM (default: compensated, the library's parity contract)")
     args = ap.parse_args()
     if args.exchange == "auto":
-        args.exchange = "halo" if int(os.environ.get("WORLD_SIZE", "1")) >= 4 else "allgather"
+        args.exchange = "push" if int(os.environ.get("WORLD_SIZE", "1")) >= 4 else "allgather"
     if args.warmup < 3 and args.impl == "native":
         args.warmup = 3
     return run_reference(args) if args.impl == "reference" else run_native(args)

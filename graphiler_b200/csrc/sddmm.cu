@@ -141,7 +141,7 @@ static int launch_u_dot_v_rows(const I *src, const I *dst, int64_t n_edges, int6
 // source rows l[src]: half the gathered bytes, and half the conversions of the exact products.  Results go to
 // z[edge id] (scattered by the row's edge ids; contiguous when edge ids are destination-sorted).  Pieces of a cut
 // row need no combination: every edge's output is independent.  Lane layout as in u_dot_v_rows_kernel.
-template <int LPR, int NV>
+template <int LPR, int NV, bool MIX>
 __global__ void __launch_bounds__(256) u_dot_v_csc_kernel(const Item *__restrict__ items, int64_t n_items,
                                                           const int32_t *__restrict__ pointer,
                                                           const int32_t *__restrict__ idx, const int32_t *__restrict__ eidx,
@@ -155,12 +155,14 @@ __global__ void __launch_bounds__(256) u_dot_v_csc_kernel(const Item *__restrict
   const int cv0 = ll * NV;
   const bool cok = cv0 < FV;
   const int lanes_per_head = DV / NV;
-  double rd[NV][2];
+  // MIX: the second half of every vector as packed fp32 products with compensated errors (the fp32 pipe shares the
+  // work); otherwise all four columns in double (one conversion and one fused multiply-add per term)
+  double rd[NV][4];
   uint64_t rp[NV];
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const float4 q = cok ? __ldg(r + (int64_t)it.row * FV + cv0 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
-    rd[v][0] = (double)q.x, rd[v][1] = (double)q.y;
+    rd[v][0] = (double)q.x, rd[v][1] = (double)q.y, rd[v][2] = (double)q.z, rd[v][3] = (double)q.w;
     rp[v] = pack2(q.z, q.w);
   }
   int next_idx = 0, next_eid = 0;
@@ -189,17 +191,26 @@ __global__ void __launch_bounds__(256) u_dot_v_csc_kernel(const Item *__restrict
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        double accd = 0.0;
-        Acc2 acc2{0, 0};
+        double acc = 0.0, acc1 = 0.0;
+        if constexpr (MIX) {
+          Acc2 acc2{0, 0};
 #pragma unroll
-        for (int v = 0; v < NV; ++v) {
-          accd = fma((double)a[u][v].x, rd[v][0], accd), accd = fma((double)a[u][v].y, rd[v][1], accd);
-          acc2.fma_exact(pack2(a[u][v].z, a[u][v].w), rp[v]);
+          for (int v = 0; v < NV; ++v) {
+            acc = fma((double)a[u][v].x, rd[v][0], acc), acc1 = fma((double)a[u][v].y, rd[v][1], acc1);
+            acc2.fma_exact(pack2(a[u][v].z, a[u][v].w), rp[v]);
+          }
+          float h0, h1, l0, l1;
+          unpack2(acc2.hi, h0, h1);
+          unpack2(acc2.lo, l0, l1);
+          acc = (acc + acc1) + (((double)h0 + (double)h1) + ((double)l0 + (double)l1));
+        } else {
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            acc = fma((double)a[u][v].x, rd[v][0], acc), acc1 = fma((double)a[u][v].y, rd[v][1], acc1);
+            acc = fma((double)a[u][v].z, rd[v][2], acc), acc1 = fma((double)a[u][v].w, rd[v][3], acc1);
+          }
+          acc += acc1;
         }
-        float h0, h1, l0, l1;
-        unpack2(acc2.hi, h0, h1);
-        unpack2(acc2.lo, l0, l1);
-        double acc = accd + (((double)h0 + (double)h1) + ((double)l0 + (double)l1));
         for (int off = 1; off < lanes_per_head; off <<= 1) acc += __shfl_xor_sync(FULL, acc, off);
         const int64_t eid = __shfl_sync(FULL, my_eid, e[u] & 31);
         if (e[u] < n && cok && (ll % lanes_per_head) == 0) z[eid * H + cv0 / DV] = (float)acc;
@@ -214,9 +225,15 @@ static int launch_u_dot_v_csc(const gphl_plan *plan, const int32_t *pointer, con
                               float *z, cudaStream_t stream) {
   const int64_t n_items = plan ? plan->n_items : n_rows;
   if (n_items == 0) return GPHL_OK;
-  u_dot_v_csc_kernel<LPR, NV><<<(unsigned)((n_items + 7) / 8), 256, 0, stream>>>(
-      plan ? plan->items : nullptr, n_items, pointer, idx, eidx, (int32_t)heads, (int32_t)fv, (int32_t)dv,
-      reinterpret_cast<const float4 *>(l), reinterpret_cast<const float4 *>(r), z);
+  const unsigned grid = (unsigned)((n_items + 7) / 8);
+  const Item *items = plan ? plan->items : nullptr;
+  const float4 *l4 = reinterpret_cast<const float4 *>(l), *r4 = reinterpret_cast<const float4 *>(r);
+  if (knob("GPHL_DOT_MIX", 0))
+    u_dot_v_csc_kernel<LPR, NV, true><<<grid, 256, 0, stream>>>(items, n_items, pointer, idx, eidx, (int32_t)heads,
+                                                                 (int32_t)fv, (int32_t)dv, l4, r4, z);
+  else
+    u_dot_v_csc_kernel<LPR, NV, false><<<grid, 256, 0, stream>>>(items, n_items, pointer, idx, eidx, (int32_t)heads,
+                                                                  (int32_t)fv, (int32_t)dv, l4, r4, z);
   return launched("u_dot_v_csc_kernel");
 }
 

@@ -361,11 +361,10 @@ extern "C" int gphl_segment_mm_tc_f32(const float *x, const float *w, const int3
   const int64_t row_tiles = (m + TC_M - 1) / TC_M + n_types;
   const int ncols_max = std::min<int>(TC_NMAX, npad);
   const size_t smem = 1024 + 3 * (size_t)A_SPLIT_BYTES + 3 * (size_t)ncols_max * 128;
-  static bool attr_set = false;
-  if (!attr_set) {
+  {
+    // the opt-in is a per-device attribute of the function: set it on every call (a process may use several GPUs)
     cudaError_t e = cudaFuncSetAttribute(segment_mm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 6 * A_SPLIT_BYTES);
     if (e != cudaSuccess) return fail(GPHL_ERR_CUDA, "segment_mm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
-    attr_set = true;
   }
   const int64_t blocks = row_tiles * ((npad + TC_NMAX - 1) / TC_NMAX);
   GPHL_REQUIRE(blocks <= 2147483647LL, "too many tiles");

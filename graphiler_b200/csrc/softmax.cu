@@ -443,11 +443,13 @@ float *g_noalloc_stats[kMaxDevices] = {nullptr};
 extern "C" int gphl_segment_softmax_noalloc_f32(const int32_t *pointer, const int32_t *edge_idx, int64_t n_rows,
                                                 int64_t heads, const float *x, float *y, void *stream) {
   GPHL_REQUIRE(n_rows >= 0 && heads >= 1, "bad sizes");
-  if (n_rows > 0 && (heads > GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS || n_rows > GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS / heads))
+  // the documented limit, checked without forming a product that could overflow: n_rows * heads <= capacity, and the
+  // head count itself below the regular entry point's limit (2^20), so that what passes here passes there too
+  if (heads >= GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS || (n_rows > 0 && n_rows > GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS / heads))
     return fail(GPHL_ERR_TOO_LARGE,
-                "segment_softmax_noalloc: n_rows * heads = %lld exceeds the built-in scratch of %d (row, head) pairs; "
-                "use gphl_segment_softmax_f32 with caller-provided scratch",
-                (long long)(n_rows * heads), GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS);
+                "segment_softmax_noalloc: %lld rows x %lld heads exceed the built-in scratch of %d (row, head) pairs "
+                "(and fewer than %d heads); use gphl_segment_softmax_f32 with caller-provided scratch",
+                (long long)n_rows, (long long)heads, GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS, GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS);
   int dev = 0;
   GPHL_CUDA(cudaGetDevice(&dev));
   GPHL_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");

@@ -88,8 +88,14 @@ class ShardedLayer:
         # after the other, so the all-gather of piece c runs while piece c+1 is being projected.  The gather buffer
         # is then piece-major - piece c of every rank, rank-major, then piece c+1 ... - so that each collective
         # fills one contiguous slab, and the shard's source indices are renumbered to that layout once, here.
-        if exchange not in ("allgather", "halo"):
-            raise ValueError("exchange must be 'allgather' or 'halo'")
+        if exchange not in ("allgather", "halo", "push"):
+            raise ValueError("exchange must be 'allgather', 'halo' or 'push'")
+        # "push" is the halo exchange with the all-to-all replaced by this library's row-gather kernel storing the
+        # requested rows straight into the receivers' buffers over NVLink (peer-mapped symmetric memory)
+        self.push = exchange == "push" and self.world > 1
+        self.push_unavailable = None
+        if exchange == "push":
+            exchange = "halo"
         self.exchange = exchange if self.world > 1 else "allgather"
         self.phase_marks = None         # set to a list to have the halo path append (name, CUDA event) after each phase
         if self.exchange == "halo":
@@ -163,6 +169,38 @@ class ShardedLayer:
         self.send_buf = torch.empty((asked.numel(), feat), dtype=dtype, device=dev)
         self.gathered = torch.empty((needed.numel(), feat), dtype=dtype, device=dev)   # compact: only the rows this shard reads
         self.halo_rows = int(needed.numel())
+        if self.push:
+            self._setup_push(feat, dtype, dev)
+
+    def _setup_push(self, feat: int, dtype, dev):
+        """Peer-mapped receive buffers for the push exchange.  Every rank allocates the same (2, R, feat) tensor in
+        symmetric memory (R = the largest halo of any rank; two slots used alternately, see project_and_gather) and
+        learns where in each peer's buffer its own rows go: receiver p keeps the rows of sender r after those of
+        senders 0..r-1, the order the all-to-all would deliver them in.  Falls back to the all-to-all, recording why,
+        if symmetric memory cannot be set up on this machine."""
+        world = self.world
+        try:
+            if not self.proj.is_cuda:
+                raise RuntimeError("peer stores need CUDA tensors")
+            import torch.distributed._symmetric_memory as symm
+            counts = torch.tensor(self.recv_counts, dtype=torch.int64, device=dev)
+            table = torch.empty((world, world), dtype=torch.int64, device=dev)         # table[p][r]: rows p receives from r
+            dist.all_gather_into_tensor(table, counts, group=self.group)
+            table = table.cpu()
+            self.push_offset = [int(table[p, :self.rank].sum()) for p in range(world)]  # my first row in p's buffer
+            rmax = max(1, int(table.sum(1).max()))
+            buf = symm.empty((2, rmax, feat), dtype=dtype, device=dev)
+            hdl = symm.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+            self._symm_handle, self._symm_local = hdl, buf
+            self.peer_bufs = [hdl.get_buffer(p, (2, rmax, feat), dtype) if p != self.rank else buf for p in range(world)]
+            self.push_slot = 0
+            self.send_offsets = [0]
+            for c in self.send_counts:
+                self.send_offsets.append(self.send_offsets[-1] + c)
+            self._push_token = torch.zeros(1, dtype=torch.int32, device=dev)
+        except Exception as ex:  # noqa: BLE001 - any failure means "use the all-to-all"
+            self.push = False
+            self.push_unavailable = repr(ex)[:300]
 
     @property
     def block_range(self):
@@ -197,6 +235,26 @@ class ShardedLayer:
             self._mark("start")
             fill(0, n_mine, self.proj[:n_mine])
             self._mark("project")
+            if self.push:
+                # One launch of the row-gather kernel per receiver, in an order that makes every step of the loop a
+                # permutation of the ranks (no receiver is the target of two senders at once); the stores go through
+                # NVLink into the receiver's slot.  Slots alternate between steps, so a sender that is one step
+                # ahead never overwrites rows a receiver is still aggregating: between two writes to the same slot
+                # lies the other slot's barrier, which a receiver enters only after that aggregation was launched on
+                # the same stream.  The barrier is a one-word NCCL all-reduce: stream-ordered, and it completes on a
+                # rank only when every rank's stores of this step have been issued before it.
+                from . import capi
+                slot, self.push_slot = self.push_slot, 1 - self.push_slot
+                for k in range(self.world):
+                    peer = (self.rank + k) % self.world
+                    a, b = self.send_offsets[peer], self.send_offsets[peer + 1]
+                    if b > a:
+                        o = self.push_offset[peer]
+                        capi.gather_rows(self.send_rows[a:b], self.proj, out=self.peer_bufs[peer][slot, o:o + (b - a)])
+                self._mark("pack")
+                dist.all_reduce(self._push_token, group=self.group)
+                self._mark("exchange")
+                return self._symm_local[slot, :self.halo_rows]
             if self.proj.is_cuda:
                 from . import capi
                 capi.gather_rows(self.send_rows, self.proj, out=self.send_buf)    # pack the requested rows

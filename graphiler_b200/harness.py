@@ -10,6 +10,7 @@ replays the network from a captured CUDA graph, which is what a launch-latency-b
 per-kernel launch overhead is amortised.
 
     python -m graphiler_b200.harness --model gat --config c1 [--repeat 200] [--cuda-graph] [--memory]
+    python -m graphiler_b200.harness --model hgt --compiled --graphiler-path <dir holding the reference's graphiler package>
 """
 from __future__ import annotations
 
@@ -144,6 +145,109 @@ def model(name: str, config: str, device: str = "cuda:0", scale: float = 1.0):
 DEFAULT_CONFIG: Dict[str, str] = {"gat": "c1", "gcn": "c2", "rgcn": "c3", "hgt": "c4"}
 
 
+# ---- the series through the reference's own compiler ----------------------------------------------------------------
+# What a Graphiler user who changes nothing gets from this operator library: the model's user-defined functions are
+# compiled by the reference's unmodified ``mpdfg_builder`` at optimisation levels 0 / 1 / 2 (the "1+compile",
+# "2+reorder", "3+fusion" steps of its breakdown(), examples/GAT/GAT.py:130-164), executed by its ``update_all`` with
+# this library installed where its wrapper loads the operator library from ($HOME/.dgl/libgraphiler.so,
+# python/graphiler/mpdfg_builder.py:11-14), then once more after this package's additional fusion patterns
+# ("4+extra-fusion").  The reference's "0-DGL-UDF" step needs DGL and is not run.  The reference's builder keeps
+# static state between builds (src/builder/builder.cpp:3,9-17,344): a model without an update function must not be
+# built after one that has one, so one process builds one model, and HGT's three-function build comes last.
+
+COMPILED_TAGS = ["1+compile", "2+reorder", "3+fusion", "4+extra-fusion", "5-layers"]
+
+
+def load_reference_wrapper(graphiler_path: Optional[str], home: Optional[str] = None):
+    """Make the reference's ``graphiler`` package importable and point it at this operator library: HOME becomes a
+    scratch directory (or ``home``) whose .dgl/ holds copies of libgraphiler.so and libgphl.so."""
+    import os
+    import shutil
+    import sys
+    import tempfile
+    from . import capi
+    home = home or tempfile.mkdtemp(prefix="gphl_home_")
+    os.environ["HOME"] = home
+    dgl = os.path.join(home, ".dgl")
+    os.makedirs(dgl, exist_ok=True)
+    for lib in (capi.TORCH_OPS_LIB, capi.KERNEL_LIB):
+        shutil.copy(str(lib), os.path.join(dgl, os.path.basename(str(lib))))
+    if graphiler_path:
+        sys.path.insert(0, graphiler_path)
+    import contextlib
+    import io
+    with contextlib.redirect_stdout(io.StringIO()):
+        import graphiler                                   # loads $HOME/.dgl/libgraphiler.so
+    return graphiler
+
+
+def compiled_series(name: str, config: str, graphiler_path: Optional[str] = None, device: str = "cuda:0",
+                    scale: float = 1.0, repeat: int = 50, memory: bool = True) -> pd.Series:
+    """Time one example model through the reference's compiler at every optimisation step (see above) and through
+    ``layers.py`` directly; returns the (tag, metric) series the reference's breakdown() returns."""
+    import contextlib
+    import io
+    from types import SimpleNamespace
+    graphiler = load_reference_wrapper(graphiler_path)
+    from . import compiled_udfs as udf
+    from .fusion import extra_fusion
+    gen_dev = device if config == "c5" else "cpu"
+    wl = synthetic.make(config, scale=scale, device=gen_dev).to(device)
+    g, p, hy = wl.graph, wl.params, wl.hyper
+    G = torch.classes.my_classes.DGLGraph(g.in_pointer, g.in_node_indices, g.in_edge_indices, g.out_pointer,
+                                          g.out_node_indices, g.out_edge_indices, g.COO_src, g.COO_dst, None, None)
+    if g.ntype_pointer is not None:
+        G.SetNtypePointer(g.ntype_pointer), G.SetNtypeCOO(g.ntype_COO)
+    if g.etype_pointer is not None:
+        G.SetEtypePointer(g.etype_pointer), G.SetEtypeCOO(g.etype_COO)
+    ndata, edata, ntd, etd, msg_params, key = {}, {}, {}, {}, (), "h"
+    if name == "gcn":                                      # one layer: projection outside, as examples/GCN/GCN.py:40-47
+        w = p["w1"] if "w1" in p else p["gcn_w"]
+        norm = g.in_degrees().clamp(min=1).float().pow(-0.5).unsqueeze(1)
+        funcs = (udf.gcn_message, udf.gcn_reduce)
+        ndata = {"h": torch.mm(wl.feats, w), "norm": norm}
+    elif name == "gat":                                    # single head over all H * D columns
+        funcs = (udf.gat_message, udf.gat_reduce)
+        f = p["fc_weight"].shape[1]
+        attn = torch.cat([p["attn_src"].reshape(f, 1), p["attn_dst"].reshape(f, 1)], 0).contiguous()
+        ndata, msg_params = {"h": wl.feats}, (p["fc_weight"], attn)
+    elif name == "rgcn":
+        funcs = (udf.rgcn_message, udf.rgcn_reduce)
+        ndata, edata, etd = {"h": wl.feats}, {"norm": wl.edata["norm"]}, {"weight": p["w1"]}
+    elif name == "hgt":
+        funcs = (udf.hgt_message, udf.hgt_reduce, udf.hgt_update)
+        ndata = {"h": wl.feats}
+        ntd = {k: p[k] for k in ("k_weight", "v_weight", "q_weight", "a_weight", "skip")}
+        etd = {k: p[k] for k in ("relation_att", "relation_msg", "relation_pri")}
+        msg_params = (float(hy["sqrt_dk"]),)
+    else:
+        raise ValueError(f"unknown model {name}")
+    log = init_log(COMPILED_TAGS, ["time", "mem"])
+    ns = SimpleNamespace(DGLGraph=G, ndata=dict(ndata), edata=edata, ntype_data=ntd, etype_data=etd)
+
+    def run(mpdfg):
+        ns.ndata = dict(ndata)
+        graphiler.update_all(ns, mpdfg, msg_params=msg_params)
+        return ns.ndata[key]
+
+    outs = {}
+    with torch.no_grad():
+        for tag, level, extra in (("1+compile", 0, False), ("2+reorder", 1, False), ("3+fusion", 2, False),
+                                  ("4+extra-fusion", 2, True)):
+            with contextlib.redirect_stdout(io.StringIO()):
+                mpdfg = graphiler.mpdfg_builder(*funcs, opt_level=level)
+                if extra:
+                    extra_fusion(mpdfg)
+            outs[tag] = bench(run, (mpdfg,), tag=tag, memory=memory, repeat=repeat, log=log)
+        net, params = model(name, config, device=device, scale=scale)
+        bench(net, params, tag="5-layers", memory=memory, repeat=repeat, log=log)
+    base = outs.get("3+fusion")
+    for tag, out in outs.items():
+        if out is not None and base is not None and tag != "3+fusion":
+            check_equal(out, base, rtol=1e-3)
+    return log
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="gat", choices=list(DEFAULT_CONFIG))
@@ -153,9 +257,19 @@ def main():
     ap.add_argument("--cuda-graph", action="store_true")
     ap.add_argument("--memory", action="store_true")
     ap.add_argument("--nvprof", action="store_true", help="bracket the timed calls with cudaProfilerStart/Stop")
+    ap.add_argument("--compiled", action="store_true",
+                    help="time the model through the reference's mpdfg_builder + update_all at every optimisation step")
+    ap.add_argument("--graphiler-path", default=None,
+                    help="directory that holds the reference's `graphiler` Python package (default: already importable)")
     a = ap.parse_args()
     config = a.config or DEFAULT_CONFIG[a.model]
     tag = f"{a.model}-{config}"
+    if a.compiled:
+        log = compiled_series(a.model, config, a.graphiler_path, scale=a.scale, repeat=a.repeat, memory=True)
+        print(json.dumps({"model": a.model, "config": config, "scale": a.scale,
+                          **{t: {"time_ms": float(log.at[(t, "time")]), "mem_mb": float(log.at[(t, "mem")])}
+                             for t in COMPILED_TAGS}}))
+        return
     log = init_log([tag], ["time", "mem", "time_cuda_graph"])
     net, params = model(a.model, config, scale=a.scale)
     out = bench(net, params, tag=tag, nvprof=a.nvprof, memory=a.memory, repeat=a.repeat, log=log, cuda_graph=a.cuda_graph)

@@ -17,8 +17,10 @@
  * reduce side); with the out_* arrays they are sources (CSR).
  *
  * Floating point: fp32 in/out ("f32") or bf16 storage with fp32 arithmetic ("bf16").  All
- * reductions use compensated (two-sum) fp32 accumulation in a fixed order, so results are
- * deterministic and independent of how rows are split or sharded.
+ * reductions accumulate exactly to the last rounding, in a fixed order: column pairs alternate between
+ * one double per column (fp64 pipe) and a compensated two-sum fp32 pair (fp32 pipe), products of two
+ * fp32 values are formed exactly (fused multiply-add in double, or the fp32 product plus its error
+ * term).  Results are deterministic and independent of how rows are split or sharded.
  */
 #ifndef GPHL_H_
 #define GPHL_H_
@@ -148,7 +150,7 @@ int gphl_segment_softmax_f32(const gphl_plan *plan, const int32_t *pointer, cons
  * whose host framework owns the allocator - and gives the same result as gphl_segment_softmax_f32
  * with plan = NULL (one warp per row, no row splitting).  The row statistics are kept in an 8 MiB
  * array inside the library image (held on every GPU that loads the library until exit), which
- * bounds the problem size: n_rows * heads <= GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS, otherwise
+ * bounds the problem size: n_rows * heads <= GPHL_SOFTMAX_NOALLOC_MAX_ROW_HEADS and heads below that number, otherwise
  * GPHL_ERR_TOO_LARGE is returned and nothing is launched.  The first call on each device looks up
  * the array's address (cudaGetSymbolAddress) with that device current; make that first call
  * before any stream capture begins.  It calls no cudaMalloc / cudaFree or allocating library

@@ -41,6 +41,16 @@ def _worker(rank, world, port, tmp):
     yh = gd.gcn_layer_sharded(sh, x[own].contiguous(), w, norm[own].contiguous(),
                               norm[sh.shard.row0:sh.shard.row1].contiguous())
     fullh = sh.gather_outputs(yh)
+    # the same exchange with the rows stored straight into the receivers' peer-mapped buffers; three steps in a row
+    # exercise the alternating receive slots.  Where symmetric memory cannot be set up it is the all-to-all again.
+    sp = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, exchange="push")
+    pushed_ok = True
+    for _ in range(3):
+        yp = gd.gcn_layer_sharded(sp, x[sp.owned_rows].contiguous(), w, norm[sp.owned_rows].contiguous(),
+                                  norm[sp.shard.row0:sp.shard.row1].contiguous())
+        pushed_ok = pushed_ok and bool(torch.equal(sp.gather_outputs(yp), single))
+    if rank == 0:
+        print("push exchange:", "peer stores" if sp.push else f"fell back to all-to-all ({sp.push_unavailable})", flush=True)
     # GAT on the same graph: z, el, er gathered, fused attention on the local rows
     p = wl.params
     sg = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, p["fc_weight"].shape[1], rank=rank, world=world)
@@ -54,7 +64,7 @@ def _worker(rank, world, port, tmp):
         # and the sparse kernels do not depend on the sharding: bit-exact
         np.save(tmp + "/ok.npy", np.array([bool(torch.equal(full, single)), full.shape[0] == g.num_nodes,
                                             bool(torch.equal(full_gat, single_gat)), bool(torch.equal(full4, single)),
-                                            bool(torch.equal(fullh, single))]))
+                                            bool(torch.equal(fullh, single)), pushed_ok]))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -187,7 +187,7 @@ def test_sddmm_u_dot_v(graph, heads, dim):
     assert torch.equal(z, z32)
 
 
-@pytest.mark.parametrize("heads,dim", [(8, 16), (1, 64), (8, 32), (4, 128), (2, 64), (64, 4), (32, 8), (16, 16), (1, 4), (2, 4),
+@pytest.mark.parametrize("heads,dim", [(8, 16), (1, 64), (8, 32), (4, 128), (2, 64), (32, 8), (16, 16), (1, 4), (2, 4),
                                        (1, 8), (4, 4), (1, 128), (8, 64)])
 @pytest.mark.parametrize("with_plan", [False, True])
 def test_sddmm_u_dot_v_row_order(graph, heads, dim, with_plan):
@@ -211,6 +211,9 @@ def test_sddmm_u_dot_v_row_order_refuses_other_shapes(graph):
     l = torch.randn(g.num_nodes, 15, device=DEV)
     with pytest.raises(capi.GphlError):
         capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_node_indices, g.in_edge_indices, l, l, 3)
+    l = torch.randn(g.num_nodes, 256, device=DEV)                       # 64 heads of 4 columns in a 1 KB row
+    with pytest.raises(capi.GphlError):
+        capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_node_indices, g.in_edge_indices, l, l, 64)
 
 
 @pytest.mark.parametrize("heads", [1, 8, 3, 40])
