@@ -21,7 +21,7 @@ ROOT = PKG.parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib"
 
-KERNEL_SOURCES = ["plan.cu", "spmm.cu", "softmax.cu", "sddmm.cu", "gather.cu", "segment_mm.cu", "segment_mm_tc.cu"]
+KERNEL_SOURCES = ["plan.cu", "spmm.cu", "softmax.cu", "sddmm.cu", "gather.cu", "segment_mm.cu", "segment_mm_tc.cu", "gspmm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

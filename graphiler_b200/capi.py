@@ -7,6 +7,7 @@ requires CUDA tensors and raises if the native library is missing.
 from __future__ import annotations
 
 import ctypes
+import weakref
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p, POINTER
 from pathlib import Path
 from typing import Optional
@@ -46,6 +47,9 @@ SIGNATURES = {
     "gphl_sddmm_u_add_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_sddmm_u_dot_v_f32_i64": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_sddmm_u_dot_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
+    "gphl_segment_mm_tc_prepare_weights": (c_int, [_P, c_int64, c_int64, c_int64, _P, _P]),
+    "gphl_segment_mm_tc_prepared_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, c_int32, _P, _P]),
+    "gphl_gspmm_f32": (c_int, [c_int32, c_int32, _P, _P, _P, c_int64, c_int64, _P, c_int64, _P, c_int64, _P, _P, _P, _P, _P, _P]),
     "gphl_sddmm_u_dot_v_csc_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_segment_softmax_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_segment_softmax_noalloc_f32": (c_int, [_P, _P, c_int64, c_int64, _P, _P, _P]),
@@ -252,6 +256,70 @@ def sddmm_u_dot_v(src, dst, l, r, heads: int, out=None):
     return z
 
 
+GSPMM_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "copy_lhs": 4, "copy_rhs": 5}
+GSPMM_REDUCERS = {"sum": 0, "max": 1, "min": 2}
+
+
+def broadcast_offsets(lhs_shape, rhs_shape):
+    """Column offsets of a broadcast binary operator on the trailing dimensions of two row tensors (the reference's
+    CalcBcastOff, src/ops/dgl_primitives/bcast.cc:20-77): the output's trailing shape is the right-aligned numpy
+    broadcast of the two; returns (out_shape, lhs_offsets, rhs_offsets) with one flat offset per output column, last
+    dimension fastest."""
+    import numpy as np
+    ls, rs = tuple(lhs_shape), tuple(rhs_shape)
+    nd = max(len(ls), len(rs))
+    ls, rs = (1,) * (nd - len(ls)) + ls, (1,) * (nd - len(rs)) + rs
+    out = tuple(max(a, b) for a, b in zip(ls, rs))
+    for a, b, o in zip(ls, rs, out):
+        if a not in (1, o) or b not in (1, o):
+            raise GphlError(f"shapes {lhs_shape} and {rhs_shape} do not broadcast")
+    idx = np.indices(out).reshape(nd, -1) if nd else np.zeros((0, 1), dtype=np.int64)
+
+    def offsets(shape):
+        off, stride = np.zeros(idx.shape[1], dtype=np.int64), 1
+        for d in range(nd - 1, -1, -1):
+            if shape[d] != 1:
+                off += idx[d] * stride
+            stride *= shape[d]
+        return off
+    return out, offsets(ls), offsets(rs)
+
+
+def gspmm(op: str, reduce: str, pointer, node_idx, edge_idx, u=None, e=None, return_args: bool = False):
+    """General g-SpMM over one side of the graph: out[v] = reduce_i op(u[node_idx[i]], e[edge_idx[i]]) with numpy
+    broadcasting over the trailing dimensions.  Returns out, or (out, arg_u, arg_e) for max / min with
+    ``return_args`` (int32; None for an operand the operator does not read)."""
+    _dev(pointer, node_idx, edge_idx, u, e)
+    if op not in GSPMM_OPS or reduce not in GSPMM_REDUCERS:
+        raise GphlError(f"gspmm: unknown operator {op!r} or reducer {reduce!r}")
+    use_l, use_r = op != "copy_rhs", op != "copy_lhs"
+    if (use_l and u is None) or (use_r and e is None):
+        raise GphlError(f"gspmm: operator {op} needs " + ("u" if use_l and u is None else "e"))
+    n_rows = pointer.numel() - 1
+    dev = pointer.device
+    if use_l and use_r:
+        trailing, lo, ro = broadcast_offsets(u.shape[1:], e.shape[1:])
+        same = tuple(u.shape[1:]) == tuple(e.shape[1:])
+        uoff = eoff = None
+        if not same:
+            uoff, eoff = torch.from_numpy(lo).to(dev), torch.from_numpy(ro).to(dev)
+    else:
+        trailing, uoff, eoff = tuple((u if use_l else e).shape[1:]), None, None
+    out_len = 1
+    for d in trailing:
+        out_len *= d
+    out = torch.empty((n_rows,) + tuple(trailing), dtype=torch.float32, device=dev)
+    want_args = return_args and reduce != "sum"
+    au = torch.zeros(out.shape, dtype=torch.int32, device=dev) if want_args and use_l else None
+    ae = torch.zeros(out.shape, dtype=torch.int32, device=dev) if want_args and use_r else None
+    with torch.cuda.device(dev):
+        _check(lib().gphl_gspmm_f32(GSPMM_OPS[op], GSPMM_REDUCERS[reduce], _ptr(pointer), _ptr(node_idx, pointer),
+                                    _ptr(edge_idx), n_rows, out_len, _ptr(u) if use_l else None, _feat(u) if use_l else 0,
+                                    _ptr(e) if use_r else None, _feat(e) if use_r else 0, _ptr(uoff), _ptr(eoff), _ptr(out),
+                                    _ptr(au), _ptr(ae), _stream(pointer)), "gspmm")
+    return (out, au, ae) if return_args and reduce != "sum" else out
+
+
 def sddmm_u_dot_v_csc(pointer, idx, edge_idx, l, r, heads: int, plan: Optional[Plan] = None, out=None):
     """u_dot_v walked in destination-row order: out[edge_idx[i], h] = sum_d l[idx[i], h, d] * r[v, h, d] for every
     position i of row v (``edge_idx`` None: edge id == position).  Raises GphlError for shapes only the COO form covers."""
@@ -343,7 +411,7 @@ def gather_rows(idx, x, idx2=None, out=None):
 
 
 def segment_mm(x, w, type_pointer, gather_idx=None, out=None, row_scale=None, relu: bool = False,
-               tensor_cores: Optional[bool] = None, workspace=None):
+               tensor_cores: Optional[bool] = None, workspace=None, _weights_owner=None):
     """y[p_t:p_{t+1}] = x[p_t:p_{t+1}] @ w[t] (rows of x optionally taken through ``gather_idx``), optionally followed
     by a per-row scale and relu.  ``tensor_cores``: None = use the tcgen05 kernel whenever the shape allows
     (k % 4 == 0) and the weights are not narrow (k <= 64 and n <= 32 go to the double-accumulating narrow kernel,
@@ -362,11 +430,17 @@ def segment_mm(x, w, type_pointer, gather_idx=None, out=None, row_scale=None, re
     with torch.cuda.device(x.device):
         if use_tc:
             need = int(lib().gphl_segment_mm_tc_workspace_bytes(t, k, n))
-            if workspace is None or workspace.numel() * workspace.element_size() < need:
-                workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
-            _check(lib().gphl_segment_mm_tc_f32(_ptr(x), _ptr(w), _ptr(type_pointer), t, m, k, n, _ptr(gather_idx),
-                                                _ptr(row_scale), 1 if relu else 0, _ptr(workspace), _ptr(y), _stream(x)),
-                   "segment_mm_tc")
+            if workspace is not None:
+                if workspace.numel() * workspace.element_size() < need:
+                    raise GphlError(f"segment_mm: the workspace must hold {need} bytes")
+                _check(lib().gphl_segment_mm_tc_f32(_ptr(x), _ptr(w), _ptr(type_pointer), t, m, k, n, _ptr(gather_idx),
+                                                    _ptr(row_scale), 1 if relu else 0, _ptr(workspace), _ptr(y), _stream(x)),
+                       "segment_mm_tc")
+            else:
+                ws = _prepared_weights(w if _weights_owner is None else _weights_owner, w, t, k, n, need, _stream(x))
+                _check(lib().gphl_segment_mm_tc_prepared_f32(_ptr(x), _ptr(ws), _ptr(type_pointer), t, m, k, n,
+                                                             _ptr(gather_idx), _ptr(row_scale), 1 if relu else 0, _ptr(y),
+                                                             _stream(x)), "segment_mm_tc_prepared")
         else:
             _check(lib().gphl_segment_mm_f32(_ptr(x), _ptr(w), _ptr(type_pointer), t, m, k, n, _ptr(gather_idx), _ptr(y),
                                              _stream(x)), "segment_mm")
@@ -375,6 +449,24 @@ def segment_mm(x, w, type_pointer, gather_idx=None, out=None, row_scale=None, re
             if relu:
                 torch.relu_(y)
     return y
+
+
+_PREPARED = {}      # id(tensor) -> (weak reference to the tensor, key, workspace); tensors compare element-wise, so not a WeakKeyDictionary
+
+
+def _prepared_weights(owner, w, t, k, n, need, stream):
+    """The split, transposed copy of a weight tensor for the tensor-core kernel, made once per (tensor object, version,
+    storage address, shape, stream): weights are constants of a layer.  An entry dies with its tensor.  ``owner`` is
+    the tensor object the caller keeps (a view of it may be what is passed as ``w``)."""
+    key = (owner._version, w.data_ptr(), tuple(w.shape), getattr(stream, "value", stream))
+    oid = id(owner)
+    hit = _PREPARED.get(oid)
+    if hit is not None and hit[0]() is owner and hit[1] == key:
+        return hit[2]
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=w.device)
+    _check(lib().gphl_segment_mm_tc_prepare_weights(_ptr(w), t, k, n, _ptr(ws), stream), "segment_mm_tc_prepare_weights")
+    _PREPARED[oid] = (weakref.ref(owner, lambda _r, oid=oid: _PREPARED.pop(oid, None)), key, ws)
+    return ws
 
 
 _ONE_TYPE = {}
@@ -390,7 +482,7 @@ def linear(x, w, row_scale=None, relu: bool = False, out=None, workspace=None):
             _ONE_TYPE.clear()
         ptr = _ONE_TYPE[key] = torch.tensor([0, x.shape[0]], dtype=torch.int32, device=x.device)
     return segment_mm(x, w.unsqueeze(0) if w.dim() == 2 else w, ptr, out=out, row_scale=row_scale, relu=relu,
-                      tensor_cores=True, workspace=workspace)
+                      tensor_cores=True, workspace=workspace, _weights_owner=w)
 
 
 def tc_wait_timeouts() -> int:

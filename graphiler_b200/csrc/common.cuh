@@ -237,10 +237,6 @@ struct VecOf<float> {
   __device__ __forceinline__ static void store(float *p, const float (&v)[4]) {
     *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
   }
-  // streaming store: the line is marked for early eviction, so an output written once does not displace gathered rows
-  __device__ __forceinline__ static void store_cs(float *p, const float (&v)[4]) {
-    __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
-  }
 };
 template <>
 struct VecOf<__nv_bfloat16> {
@@ -262,15 +258,6 @@ struct VecOf<__nv_bfloat16> {
       w[i] = *reinterpret_cast<uint32_t *>(&b);
     }
     *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-  __device__ __forceinline__ static void store_cs(__nv_bfloat16 *p, const float (&v)[8]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-      w[i] = *reinterpret_cast<uint32_t *>(&b);
-    }
-    __stcs(reinterpret_cast<uint4 *>(p), make_uint4(w[0], w[1], w[2], w[3]));
   }
 };
 

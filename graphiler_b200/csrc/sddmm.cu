@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__
   const int cv0 = ll * NV;                                   // first vector of this lane
   const bool cok = cv0 < FV;                                 // FV is a multiple of NV: all or none of the lane's vectors
   const int lanes_per_head = DV / NV;
+  const bool writer = cok && (ll % lanes_per_head) == 0;     // hoisted: integer division by a run-time value is dear
+  const int my_head = cv0 / DV;
   const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   for (int64_t base = warp_id * 32; base < n_edges; base += n_warps * 32) {
@@ -117,8 +119,10 @@ __global__ void __launch_bounds__(256) u_dot_v_rows_kernel(const I *__restrict__
         unpack2(acc2.hi, h0, h1);
         unpack2(acc2.lo, l0, l1);
         double acc = accd + (((double)h0 + (double)h1) + ((double)l0 + (double)l1));
-        for (int off = 1; off < lanes_per_head; off <<= 1) acc += __shfl_xor_sync(FULL, acc, off);   // a power of two <= LPR
-        if (e[u] < n && cok && (ll % lanes_per_head) == 0) z[(base + e[u]) * H + cv0 / DV] = (float)acc;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1)
+          if (off < lanes_per_head) acc += __shfl_xor_sync(FULL, acc, off);      // a power of two <= LPR; uniform condition
+        if (e[u] < n && writer) z[(base + e[u]) * H + my_head] = (float)acc;
       }
     }
   }
@@ -155,6 +159,8 @@ __global__ void __launch_bounds__(256) u_dot_v_csc_kernel(const Item *__restrict
   const int cv0 = ll * NV;
   const bool cok = cv0 < FV;
   const int lanes_per_head = DV / NV;
+  const bool writer = cok && (ll % lanes_per_head) == 0;     // hoisted: integer division by a run-time value is dear
+  const int my_head = cv0 / DV;
   // MIX: the second half of every vector as packed fp32 products with compensated errors (the fp32 pipe shares the
   // work); otherwise all four columns in double (one conversion and one fused multiply-add per term)
   double rd[NV][4];
@@ -211,9 +217,11 @@ __global__ void __launch_bounds__(256) u_dot_v_csc_kernel(const Item *__restrict
           }
           acc += acc1;
         }
-        for (int off = 1; off < lanes_per_head; off <<= 1) acc += __shfl_xor_sync(FULL, acc, off);
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1)
+          if (off < lanes_per_head) acc += __shfl_xor_sync(FULL, acc, off);      // uniform condition
         const int64_t eid = __shfl_sync(FULL, my_eid, e[u] & 31);
-        if (e[u] < n && cok && (ll % lanes_per_head) == 0) z[eid * H + cv0 / DV] = (float)acc;
+        if (e[u] < n && writer) z[eid * H + my_head] = (float)acc;
       }
     }
   }
@@ -413,6 +421,8 @@ __global__ void __launch_bounds__(256) head_scores_rows_kernel(const float4 *__r
   const int cv0 = ll * NV;
   const bool cok = cv0 < FV;
   const int lanes_per_head = DV / NV;
+  const bool writer = cok && (ll % lanes_per_head) == 0;     // hoisted: integer division by a run-time value is dear
+  const int my_head = cv0 / DV;
   double ps[NV][4];                                      // this lane's columns of a_src, widened once
   float4 pd[NV];
 #pragma unroll
@@ -452,9 +462,9 @@ __global__ void __launch_bounds__(256) head_scores_rows_kernel(const float4 *__r
         s += __shfl_xor_sync(FULL, s, off);
         d += __shfl_xor_sync(FULL, d, off);
       }
-      if (r[u] < n && cok && (ll % lanes_per_head) == 0) {
-        el[r[u] * H + cv0 / DV] = (float)s;
-        er[r[u] * H + cv0 / DV] = (float)d;
+      if (r[u] < n && writer) {
+        el[r[u] * H + my_head] = (float)s;
+        er[r[u] * H + my_head] = (float)d;
       }
     }
   }

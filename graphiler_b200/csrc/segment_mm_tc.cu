@@ -10,13 +10,17 @@
 // output.  The reduction dimension is processed in slabs of 64: all threads load the slab of x
 // (16-byte loads, optionally through a row index), split it and store the three bf16 copies into
 // shared memory in the 128-byte-swizzled K-major layout the tensor core reads; the slab of the
-// pre-split, pre-transposed weights is copied next to it; one elected thread issues the 24
-// tcgen05.mma instructions of the slab and commits them to an mbarrier.  The next slab's loads of x
+// pre-split, pre-transposed weights arrives next to it by TMA (cp.async.bulk.tensor.2d with the 128-byte
+// swizzle, from a tensor map over the weight workspace in this GPU's own memory; no multicast), one or two
+// slabs ahead of the tensor core; one elected thread issues the 24 tcgen05.mma instructions of the slab
+// and commits them to an mbarrier.  The next slab's loads of x
 // are issued before that barrier is waited on, and two or three blocks share an SM, so loads,
 // splitting and tensor work overlap.  The accumulator (128 lanes x <=128 columns) is read back
 // with tcgen05.ld and stored with 16-byte stores.  Every wait is bounded: if a barrier does not
 // complete, the block records it in a device flag, waits once more for what it issued, frees its
 // tensor memory and returns.
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace gphl {
@@ -49,6 +53,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (done) return true;
   }
   return false;
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One box of the tensor map (64 K-values x box rows, 128-byte swizzle) into shared memory; completion is counted in
+// bytes on `bar`.  x is a multiple of 64 bf16 elements = 128 bytes, so the 16-byte alignment rule of the inner
+// coordinate always holds.  The map covers the weight workspace of the launching GPU only.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+               : "memory");
 }
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 B apart.
@@ -122,11 +138,14 @@ struct TcArgs {
   float *y;
   int64_t m;
   int32_t T, K, N, Kpad, Npad, relu;
+  int32_t stages;            // weight slabs in shared memory (1 or 2)
+  int32_t box_rows;          // rows of one TMA box = min(128, Npad)
 };
 
-__global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a) {
+__global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t s_bar;
+  __shared__ uint64_t s_full[2];
   __shared__ uint32_t s_tmem;
   __shared__ int s_seg, s_row0, s_rows, s_failed;
 
@@ -169,9 +188,11 @@ __global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a) {
 
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t *sA = smem;                                      // 3 x (128 rows x 128 B)
-  uint8_t *sB = smem + 3 * A_SPLIT_BYTES;                  // 3 x (ncols rows x 128 B)
-  const int b_split_bytes = ncols * 128;
+  uint8_t *sB = smem + 3 * A_SPLIT_BYTES;                  // stages x 3 x (box_rows rows x 128 B)
+  const int b_split_bytes = a.box_rows * 128;              // a box is always whole; rows beyond ncols are not multiplied
+  const int b_stage_bytes = 3 * b_split_bytes;
   const uint32_t bar = smem_u32(&s_bar);
+  const uint32_t full0 = smem_u32(&s_full[0]);
 
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(tmem_cols)
@@ -179,6 +200,8 @@ __global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     if (lane == 0) {
       mbar_init(bar, 1);
+      mbar_init(full0, 1);
+      mbar_init(full0 + 8, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
   }
@@ -210,22 +233,27 @@ __global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a) {
 
   const int nslabs = a.Kpad / TC_SLAB;
   const uint32_t idesc = umma_idesc(ncols);
-  const __nv_bfloat16 *wsplit = a.ws + ((int64_t)seg * a.Npad + n0) * a.Kpad;
-  const int64_t wsplit_stride = (int64_t)a.T * a.Npad * a.Kpad;
+  // weight slabs: slab j goes to stage j % S; with S = 2 the copy of slab s + 1 is issued as soon as the tensor core
+  // has finished slab s - 1, and runs while slab s is split, stored and multiplied
+  const int S = a.stages, L = S - 1;
+  const int wrow0 = seg * a.Npad + n0, wplane = a.T * a.Npad;      // row of this tile in split 0; rows per split
+  int issued = 0, consumed = 0;                                     // thread 0 only
+  auto issue_weights = [&](int j) {
+    const uint32_t fb = full0 + 8 * (j % S);
+    const uint32_t dst = smem_u32(sB) + (uint32_t)((j % S) * b_stage_bytes);
+    mbar_expect_tx(fb, (uint32_t)b_stage_bytes);
+#pragma unroll
+    for (int sp = 0; sp < 3; ++sp) tma_load_2d(dst + sp * b_split_bytes, &wmap, j * TC_SLAB, sp * wplane + wrow0, fb);
+    ++issued;
+  };
+  if (tid == 0)
+    for (int j = 0; j < L && j < nslabs; ++j) issue_weights(j);
   load_slab(0);
   for (int s = 0; s < nslabs; ++s) {
     // the tensor core must be done reading the previous slab before it is overwritten; a wait that runs
     // out is recorded and acted on by all threads together after the next block-wide barrier
     if (s > 0 && !mbar_wait(bar, (uint32_t)((s - 1) & 1))) s_failed = 1;
-    // weight slab: 3 copies x ncols rows x 8 chunks, already bf16 and K-major in global memory; asynchronous
-    // 16-byte copies straight into the swizzled layout
-    for (int sp = 0; sp < 3; ++sp) {
-      const __nv_bfloat16 *wsrc = wsplit + sp * wsplit_stride + s * TC_SLAB + c * 8;
-      for (int n = tid >> 3; n < ncols; n += TC_THREADS / 8) {
-        const uint32_t dst = smem_u32(sB + sp * b_split_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(wsrc + (int64_t)n * a.Kpad) : "memory");
-      }
-    }
+    if (tid == 0 && s + L < nslabs && !s_failed) issue_weights(s + L);
     // x slab: split and store the three bf16 copies (swizzled: 16-byte chunk c of row r goes to chunk c ^ (r % 8))
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -240,29 +268,37 @@ __global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a) {
       *reinterpret_cast<uint4 *>(sA + A_SPLIT_BYTES + off) = o2;
       *reinterpret_cast<uint4 *>(sA + 2 * A_SPLIT_BYTES + off) = o3;
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the stores visible to the tensor core
     if (s + 1 < nslabs) load_slab((s + 1) * TC_SLAB);              // in flight while the tensor core works
     __syncthreads();
     if (s_failed) break;                                           // uniform: written before the barrier
     if (tid == 0) {
+      const bool arrived = mbar_wait(full0 + 8 * (s % S), (uint32_t)((s / S) & 1));   // this slab's weights
+      ++consumed;
+      if (!arrived) s_failed = 1;                                  // seen by everyone after the next barrier
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
+      const uint32_t aA = smem_u32(sA), aB = smem_u32(sB) + (uint32_t)((s % S) * b_stage_bytes);
       // corrections (smallest first) x1w3, x3w1, x2w2, x1w2, x2w1 into the second accumulator, x1w1 into the first
       const int pa[6] = {0, 2, 1, 0, 1, 0}, pb[6] = {2, 0, 1, 1, 0, 0};
+      if (arrived) {
 #pragma unroll
-      for (int p = 0; p < 6; ++p) {
+        for (int p = 0; p < 6; ++p) {
 #pragma unroll
-        for (int kk = 0; kk < TC_SLAB / 16; ++kk) {
-          const uint64_t da = umma_desc(aA + pa[p] * A_SPLIT_BYTES + kk * 32);
-          const uint64_t db = umma_desc(aB + pb[p] * b_split_bytes + kk * 32);
-          if (p < 5) umma_bf16(tmem + acc_cols, da, db, idesc, (s > 0 || p > 0 || kk > 0) ? 1u : 0u);
-          else umma_bf16(tmem, da, db, idesc, (s > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < TC_SLAB / 16; ++kk) {
+            const uint64_t da = umma_desc(aA + pa[p] * A_SPLIT_BYTES + kk * 32);
+            const uint64_t db = umma_desc(aB + pb[p] * b_split_bytes + kk * 32);
+            if (p < 5) umma_bf16(tmem + acc_cols, da, db, idesc, (s > 0 || p > 0 || kk > 0) ? 1u : 0u);
+            else umma_bf16(tmem, da, db, idesc, (s > 0 || kk > 0) ? 1u : 0u);
+          }
         }
       }
+      // committed in either case, so that the other threads' wait for this slab ends
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
     }
   }
+  // copies that were issued but never waited for (only after a failed wait) must land before the block leaves
+  if (tid == 0)
+    for (int j = consumed; j < issued; ++j) mbar_wait(full0 + 8 * (j % S), (uint32_t)((j / S) & 1));
   // wait for the last committed slab (bounded); on a timeout, count it once per block
   if (!mbar_wait(bar, (uint32_t)((nslabs - 1) & 1))) s_failed = 1;
   __syncthreads();
@@ -338,38 +374,101 @@ extern "C" int64_t gphl_segment_mm_tc_workspace_bytes(int64_t n_types, int64_t k
   return 3 * n_types * npad * kpad * (int64_t)sizeof(__nv_bfloat16);
 }
 
-extern "C" int gphl_segment_mm_tc_f32(const float *x, const float *w, const int32_t *type_pointer, int64_t n_types,
-                                      int64_t m, int64_t k, int64_t n, const int64_t *gather_idx, const float *row_scale,
-                                      int32_t relu, void *workspace, float *y, void *stream_) {
-  GPHL_REQUIRE(n_types >= 0 && m >= 0 && k >= 0 && n >= 0, "negative size");
-  GPHL_REQUIRE(m < INT32_MAX && k < (1 << 16) && n < (1 << 16) && n_types < (1 << 20), "size out of range");
-  if (m == 0 || n == 0 || n_types == 0) return GPHL_OK;
-  GPHL_REQUIRE(x && w && type_pointer && y && workspace, "null pointer argument");
-  if (k % 4 != 0 || !aligned16(x) || !aligned16(workspace) || !aligned16(y))
-    return fail(GPHL_ERR_UNSUPPORTED, "segment_mm_tc needs k %% 4 == 0 and 16-byte aligned x, y and workspace");
+// Tensor map over the split weights: a (3 * T * Npad) x Kpad matrix of bf16, K contiguous; one box = 64 K-values
+// (128 bytes, the swizzle span) x box_rows rows.  cuTensorMapEncodeTiled is reached through the runtime's driver
+// entry-point query, so the library does not link against the driver.
+namespace gphl {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+}  // namespace gphl
+
+// Splits and transposes the weights into `workspace` (gphl_segment_mm_tc_workspace_bytes): the part of the typed
+// linear that depends on the weights alone.  A caller whose weights are constants of a layer does it once and calls
+// gphl_segment_mm_tc_prepared_f32 afterwards.
+extern "C" int gphl_segment_mm_tc_prepare_weights(const float *w, int64_t n_types, int64_t k, int64_t n, void *workspace,
+                                                  void *stream_) {
+  GPHL_REQUIRE(n_types >= 0 && k >= 0 && n >= 0, "negative size");
+  GPHL_REQUIRE(k < (1 << 16) && n < (1 << 16) && n_types < (1 << 20), "size out of range");
+  if (n == 0 || n_types == 0 || k == 0) return GPHL_OK;
+  GPHL_REQUIRE(w && workspace && aligned16(workspace), "null or unaligned pointer argument");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int32_t kpad = (int32_t)((k + TC_SLAB - 1) / TC_SLAB * TC_SLAB), npad = (int32_t)((n + 15) / 16 * 16);
   const int64_t total = n_types * (int64_t)npad * kpad;
   split_weights_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, 148 * 16), 256, 0, stream>>>(
       w, (int32_t)n_types, (int32_t)k, (int32_t)n, kpad, npad, static_cast<__nv_bfloat16 *>(workspace));
-  int rc = launched("split_weights_kernel");
-  if (rc != GPHL_OK) return rc;
+  return launched("split_weights_kernel");
+}
+
+extern "C" int gphl_segment_mm_tc_prepared_f32(const float *x, const void *workspace, const int32_t *type_pointer,
+                                               int64_t n_types, int64_t m, int64_t k, int64_t n, const int64_t *gather_idx,
+                                               const float *row_scale, int32_t relu, float *y, void *stream_) {
+  GPHL_REQUIRE(n_types >= 0 && m >= 0 && k >= 0 && n >= 0, "negative size");
+  GPHL_REQUIRE(m < INT32_MAX && k < (1 << 16) && n < (1 << 16) && n_types < (1 << 20), "size out of range");
+  if (m == 0 || n == 0 || n_types == 0) return GPHL_OK;
+  GPHL_REQUIRE(x && type_pointer && y && workspace, "null pointer argument");
+  if (k % 4 != 0 || k == 0 || !aligned16(x) || !aligned16(workspace) || !aligned16(y))
+    return fail(GPHL_ERR_UNSUPPORTED, "segment_mm_tc needs k %% 4 == 0 and 16-byte aligned x, y and workspace");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int32_t kpad = (int32_t)((k + TC_SLAB - 1) / TC_SLAB * TC_SLAB), npad = (int32_t)((n + 15) / 16 * 16);
   TcArgs a{};
   a.x = x, a.ws = static_cast<const __nv_bfloat16 *>(workspace), a.ptr = type_pointer, a.gather = gather_idx;
   a.row_scale = row_scale, a.y = y, a.m = m, a.T = (int32_t)n_types, a.K = (int32_t)k, a.N = (int32_t)n;
   a.Kpad = kpad, a.Npad = npad, a.relu = relu;
-  const int64_t row_tiles = (m + TC_M - 1) / TC_M + n_types;
-  const int ncols_max = std::min<int>(TC_NMAX, npad);
-  const size_t smem = 1024 + 3 * (size_t)A_SPLIT_BYTES + 3 * (size_t)ncols_max * 128;
+  a.box_rows = std::min<int>(TC_NMAX, npad);
+  // two weight slabs in shared memory where two blocks still share an SM (boxes of at most 64 rows: 1 + 48 + 2 x 24
+  // KB); with 128-row boxes a second slab would leave one block per SM, and two blocks with one slab each overlap
+  // their phases better (measured)
+  const size_t stage_bytes = 3 * (size_t)a.box_rows * 128;
+  const int forced = knob("GPHL_TC_STAGES", 0);
+  a.stages = forced ? std::min(2, std::max(1, forced)) : (a.box_rows <= 64 ? 2 : 1);
+  const size_t smem = 1024 + 3 * (size_t)A_SPLIT_BYTES + a.stages * stage_bytes;
+
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return fail(GPHL_ERR_CUDA, "segment_mm_tc: cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap wmap;
+  const cuuint64_t gdim[2] = {(cuuint64_t)kpad, (cuuint64_t)(3 * n_types * npad)};
+  const cuuint64_t gstride[1] = {(cuuint64_t)kpad * sizeof(__nv_bfloat16)};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_SLAB, (cuuint32_t)a.box_rows};
+  const cuuint32_t estride[2] = {1, 1};
+  const CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(workspace), gdim, gstride, box, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return fail(GPHL_ERR_CUDA, "segment_mm_tc: cuTensorMapEncodeTiled failed (%d)", (int)cr);
   {
     // the opt-in is a per-device attribute of the function: set it on every call (a process may use several GPUs)
-    cudaError_t e = cudaFuncSetAttribute(segment_mm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 6 * A_SPLIT_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(segment_mm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         1024 + 3 * A_SPLIT_BYTES + 2 * 3 * TC_NMAX * 128);
     if (e != cudaSuccess) return fail(GPHL_ERR_CUDA, "segment_mm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
   }
+  const int64_t row_tiles = (m + TC_M - 1) / TC_M + n_types;
   const int64_t blocks = row_tiles * ((npad + TC_NMAX - 1) / TC_NMAX);
   GPHL_REQUIRE(blocks <= 2147483647LL, "too many tiles");
-  segment_mm_tc_kernel<<<(unsigned)blocks, TC_THREADS, smem, stream>>>(a);
+  segment_mm_tc_kernel<<<(unsigned)blocks, TC_THREADS, smem, stream>>>(a, wmap);
   return launched("segment_mm_tc_kernel");
+}
+
+extern "C" int gphl_segment_mm_tc_f32(const float *x, const float *w, const int32_t *type_pointer, int64_t n_types,
+                                      int64_t m, int64_t k, int64_t n, const int64_t *gather_idx, const float *row_scale,
+                                      int32_t relu, void *workspace, float *y, void *stream_) {
+  if (m == 0 || n == 0 || n_types == 0) return GPHL_OK;
+  GPHL_REQUIRE(w != nullptr, "null pointer argument");
+  if (k % 4 != 0 || k <= 0 || !aligned16(x) || !aligned16(workspace) || !aligned16(y))
+    return fail(GPHL_ERR_UNSUPPORTED, "segment_mm_tc needs k %% 4 == 0 and 16-byte aligned x, y and workspace");
+  int rc = gphl_segment_mm_tc_prepare_weights(w, n_types, k, n, workspace, stream_);
+  if (rc != GPHL_OK) return rc;
+  return gphl_segment_mm_tc_prepared_f32(x, workspace, type_pointer, n_types, m, k, n, gather_idx, row_scale, relu, y, stream_);
 }
 
 // Self-test of the bounded wait: one warp waits, with a short poll limit, on an mbarrier that nothing ever

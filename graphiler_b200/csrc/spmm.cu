@@ -33,7 +33,6 @@ struct GatherArgs {
   float slope;
   int32_t relu;          // epilogue: max(., 0)
   int32_t exact;         // 1: compensated accumulation (default), 0: plain fp32 adds
-  int32_t stream;        // 1: index loads and output stores carry the evict-first hint
   int32_t wvec;          // per-head arrays (w | el, er, stats) can be read four heads at a time
   int64_t n_long;        // items [0, n_long) are longer than GPHL_SHORT_ITEM positions; -1: unknown (no plan)
   int32_t F, FV, H, DV;  // columns, 16-byte vectors per row, heads, vectors per head
@@ -213,12 +212,11 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
   float *wsm = smem_w + (size_t)warp * 32 * a.H;
 
   int next_idx = 0;
-  if (it.begin + lane < it.end) next_idx = a.stream ? __ldcs(a.idx + it.begin + lane) : __ldg(a.idx + it.begin + lane);
+  if (it.begin + lane < it.end) next_idx = __ldg(a.idx + it.begin + lane);
   for (int base = it.begin; base < it.end; base += 32) {
     const int n = min(32, it.end - base);
     const int my_idx = next_idx;
-    if (base + 32 + lane < it.end)                                               // prefetch the next batch
-      next_idx = a.stream ? __ldcs(a.idx + base + 32 + lane) : __ldg(a.idx + base + 32 + lane);
+    if (base + 32 + lane < it.end) next_idx = __ldg(a.idx + base + 32 + lane);   // prefetch the next batch
     if (MODE != COPY) {
       __syncwarp();
       if (lane < n) {
@@ -350,8 +348,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
         if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
         if (a.relu) o[k] = fmaxf(o[k], 0.f);
       }
-      if (a.stream) VecOf<T>::store_cs(y + (int64_t)cv[v] * VEC, o);
-      else VecOf<T>::store(y + (int64_t)cv[v] * VEC, o);
+      VecOf<T>::store(y + (int64_t)cv[v] * VEC, o);
     }
   } else {
     float *hi = a.scratch + (int64_t)(2 * it.slot) * a.plane;
@@ -566,130 +563,6 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_sliced_kernel(GatherArg
   }
 }
 
-// ---- whole wide rows, one warp per item, no cross-lane traffic in the loop --------------------------------------
-// Rows of 32 * NV vectors (512 B per NV): lane l holds vectors l, l + 32, ...; the warp walks the item's positions in
-// order, U rows in flight, every lane reading the same index word (one broadcast access) instead of taking it from a
-// neighbour by shuffle.  The indices of the next U positions are fetched while the current rows are summed.
-template <typename T, int NV, int U, int EXACT>
-__global__ void __launch_bounds__(WARPS * 32) gather_sum_wide_kernel(GatherArgs a) {
-  constexpr int VEC = VecOf<T>::N, VP = VEC / 2;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t item_id = (int64_t)blockIdx.x * WARPS + warp;
-  if (item_id >= a.n_items) return;
-  const Item it = fetch_item(a.items, a.pointer, item_id);
-  bool cok[NV];
-#pragma unroll
-  for (int v = 0; v < NV; ++v) cok[v] = v * 32 + lane < a.FV;
-  AccT<EXACT> acc[NV][VP];
-#pragma unroll
-  for (int v = 0; v < NV; ++v)
-#pragma unroll
-    for (int k = 0; k < VP; ++k) {
-      acc[v][k].hi = 0;
-      if constexpr (EXACT) acc[v][k].lo = 0;
-    }
-  const char *xb = static_cast<const char *>(a.x) + (size_t)lane * 16;
-  const uint32_t row_bytes = (uint32_t)a.FV * 16u;
-  const int32_t *ip = a.idx + it.begin;
-  const int cnt = it.end - it.begin;
-  auto load_row = [&](uint4 (&raw)[NV], int src) {
-    const char *row = xb + (uint64_t)(uint32_t)src * row_bytes;
-#pragma unroll
-    for (int v = 0; v < NV; ++v)
-      raw[v] = cok[v] ? __ldg(reinterpret_cast<const uint4 *>(row + v * 512)) : make_uint4(0, 0, 0, 0);
-  };
-  auto add_row = [&](const uint4 (&raw)[NV]) {
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      uint64_t val[VP];
-      unpack_pairs<T>(raw[v], val);
-#pragma unroll
-      for (int k = 0; k < VP; ++k) acc[v][k].add(val[k], v * VP + k);
-    }
-  };
-  int i = 0;
-  int s[U];
-  if (U <= cnt) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) s[u] = __ldg(ip + u);
-  }
-#pragma unroll 1
-  for (; i + U <= cnt; i += U) {
-    uint4 raw[U][NV];
-#pragma unroll
-    for (int u = 0; u < U; ++u) load_row(raw[u], s[u]);
-    if (i + 2 * U <= cnt) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) s[u] = __ldg(ip + i + U + u);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) add_row(raw[u]);
-  }
-  if (i < cnt) {                                   // the last cnt % U positions, all in flight together
-    uint4 raw[U][NV];
-#pragma unroll
-    for (int u = 0; u < U - 1; ++u)
-      if (i + u < cnt) load_row(raw[u], __ldg(ip + i + u));
-#pragma unroll
-    for (int u = 0; u < U - 1; ++u)
-      if (i + u < cnt) add_row(raw[u]);
-  }
-
-  if (it.slot < 0) {
-    T *y = static_cast<T *>(a.y) + (int64_t)it.row * a.F;
-    const float scale = a.dst_scale ? __ldg(a.dst_scale + it.row) : 1.f;
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      if (!cok[v]) continue;
-      float o[VEC];
-#pragma unroll
-      for (int k = 0; k < VP; ++k) unpack2(acc[v][k].value(v * VP + k), o[2 * k], o[2 * k + 1]);
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        if (a.dst_scale) o[k] = __fmul_rn(o[k], scale);
-        if (a.relu) o[k] = fmaxf(o[k], 0.f);
-      }
-      VecOf<T>::store(y + (int64_t)(v * 32 + lane) * VEC, o);
-    }
-  } else {
-    float *hi = a.scratch + (int64_t)(2 * it.slot) * a.plane;
-    float *lo = hi + a.plane;
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      if (!cok[v]) continue;
-#pragma unroll
-      for (int k = 0; k < VP; ++k) {
-        float h0, h1, l0, l1;
-        acc[v][k].planes(h0, h1, l0, l1, v * VP + k);
-        const int c = (v * 32 + lane) * VEC + 2 * k;
-        hi[c] = h0, hi[c + 1] = h1, lo[c] = l0, lo[c + 1] = l1;
-      }
-    }
-  }
-}
-
-template <typename T, int NV, int U>
-static int launch_wide_u(const GatherArgs &a, cudaStream_t stream) {
-  const unsigned grid = (unsigned)((a.n_items + WARPS - 1) / WARPS);
-  const int forced = knob("GPHL_ACC", 0);
-  const int kind = !a.exact ? 0 : forced ? forced : 3;
-  if (kind == 0) gather_sum_wide_kernel<T, NV, U, 0><<<grid, WARPS * 32, 0, stream>>>(a);
-  else if (kind == 1) gather_sum_wide_kernel<T, NV, U, 1><<<grid, WARPS * 32, 0, stream>>>(a);
-  else if (kind == 2) gather_sum_wide_kernel<T, NV, U, 2><<<grid, WARPS * 32, 0, stream>>>(a);
-  else gather_sum_wide_kernel<T, NV, U, 3><<<grid, WARPS * 32, 0, stream>>>(a);
-  return launched("gather_sum_wide_kernel");
-}
-
-template <typename T, int NV>
-static int launch_wide(const GatherArgs &a, cudaStream_t stream) {
-  const int u = knob("GPHL_WIDE_U", NV == 1 ? 4 : 2);
-  if (u >= 8 && NV == 1) return launch_wide_u<T, NV, 8>(a, stream);
-  if (u >= 4 && NV <= 2) return launch_wide_u<T, NV, 4>(a, stream);
-  if (u >= 3 && NV <= 2) return launch_wide_u<T, NV, 3>(a, stream);
-  if (u >= 2) return launch_wide_u<T, NV, 2>(a, stream);
-  return launch_wide_u<T, NV, 1>(a, stream);
-}
-
 template <typename T, int LPR>
 static int launch_sliced(const GatherArgs &a, cudaStream_t stream) {
   // long items: a warp per (item, slice); short items: LPR lanes per (item, slice)
@@ -714,13 +587,20 @@ static int launch_sliced(const GatherArgs &a, cudaStream_t stream) {
   return GPHL_OK;
 }
 
-// Slice width (in 16-byte vectors) for the unweighted sum, 0 = one pass over whole rows (the default: on the 62 M-edge,
-// 256-column gather one pass takes 6.1 ms, two slices 6.7 ms, four 8.2 ms, eight 14.5 ms: with a warp per item the
-// fixed cost of a short item is paid once per slice and outweighs the better cache hit rate).  Measurement builds
-// choose the width with GPHL_SLICE_LPR.
-static int slice_lanes(int32_t /*FV*/) {
+// Which unweighted sums take the sliced kernels (slice width in 16-byte vectors; 0 = the general kernel, one pass
+// over whole rows).  Measured on the 62 M-edge graph with 256 columns.  fp32 (1 KB rows): one pass 6.0 ms, two slices
+// of 32 vectors 6.0-6.4 ms, four of 16 6.1 ms, eight of 8 9.2 ms: the better cache hit rate of narrow slices is paid
+// for with one more pass over the index array and one more fixed cost per short row and slice, so fp32 stays on the
+// general kernel.  bf16 storage (512-byte rows = one slice of 32 vectors): 4.1 ms against 5.1 ms, because the sliced
+// pair (a warp per long item, a plain per-row loop for short items, indices read directly instead of exchanged by
+// shuffle) spends fewer instructions per row; it is the default there.  The choice depends on the storage type and the
+// row width only, never on the number of rows, so that a shard of any size takes the same kernel and sums in the
+// same order.  Measurement builds choose the width with GPHL_SLICE_LPR (-1: never).
+template <typename T>
+static int slice_lanes(int32_t FV) {
   const int forced = knob("GPHL_SLICE_LPR", 0);
-  return forced < 0 ? 0 : forced;
+  if (forced) return forced < 0 ? 0 : forced;
+  return (sizeof(T) == 2 && FV == 32) ? 32 : 0;
 }
 
 // Any shape / alignment: one thread per (item, column), serial over the piece.
@@ -842,7 +722,6 @@ static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t
   constexpr int VEC = VecOf<T>::N;
   if (a.n_items == 0 || a.F == 0) return GPHL_OK;
   a.n_long = -1;
-  a.stream = knob("GPHL_STREAM_HINT", 0);
   if (plan) {
     a.items = plan->items;
     a.n_items = plan->n_items;
@@ -862,12 +741,8 @@ static int dispatch(const gphl_plan *plan, GatherArgs a, int32_t D, cudaStream_t
     a.wvec = 0;
     if (MODE == MUL_E) a.wvec = a.H % 4 == 0 && aligned16(a.w);
     if (MODE == GAT) a.wvec = a.H % 4 == 0 && aligned16(a.el) && aligned16(a.er) && aligned16(a.stats);
-    const int slice = (MODE == COPY) ? slice_lanes(a.FV) : 0;
-    if (MODE == COPY && a.FV >= 32 && a.FV <= 128 && knob("GPHL_WIDE", 0)) {
-      if (a.FV <= 32) rc = launch_wide<T, 1>(a, stream);
-      else if (a.FV <= 64) rc = launch_wide<T, 2>(a, stream);
-      else rc = launch_wide<T, 4>(a, stream);
-    } else if (MODE == COPY && slice > 0) {
+    const int slice = (MODE == COPY) ? slice_lanes<T>(a.FV) : 0;
+    if (MODE == COPY && slice > 0) {
       if (slice >= 32) rc = launch_sliced<T, 32>(a, stream);
       else if (slice >= 16) rc = launch_sliced<T, 16>(a, stream);
       else if (slice >= 8) rc = launch_sliced<T, 8>(a, stream);

@@ -10,6 +10,8 @@
 // src/ops/dgl_primitives/spmm.cu:391-406, src/ops/dgl_primitives/sddmm.cu:131-134.
 // `int? t` is bound as optional<int64_t>: current PyTorch rejects optional<ScalarType> for it.
 #include <cstdlib>
+#include <vector>
+#include <mutex>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/custom_class.h>
@@ -438,6 +440,44 @@ Tensor gat_fused(Tensor el, Tensor er, Tensor z, double slope, const GraphPtr &g
 }
 
 // ---- typed linear -----------------------------------------------------------------------------
+// Split weights of the tensor-core typed linear, kept per weight tensor: weights are constants of a layer, so the
+// split kernel runs once per (tensor, version) instead of once per call.  An entry is valid while the very same
+// TensorImpl is alive (a weak reference keeps its address from being reused), its version counter and storage
+// address are unchanged and the call comes on the stream the workspace was written on; anything else is a miss.
+struct PreparedWeights {
+  c10::weak_intrusive_ptr<c10::TensorImpl> impl;
+  const void *data;
+  uint32_t version;
+  int64_t t, k, n;
+  void *stream;
+  Tensor ws;
+};
+Tensor prepared_weights(const Tensor &wc, int64_t t, int64_t k, int64_t n, void *stream) {
+  static std::mutex mu;
+  static std::vector<PreparedWeights> cache;
+  const bool trackable = !wc.is_inference();
+  std::lock_guard<std::mutex> lock(mu);
+  if (trackable) {
+    for (size_t i = 0; i < cache.size(); ++i) {
+      PreparedWeights &e = cache[i];
+      if (e.impl._unsafe_get_target() == wc.unsafeGetTensorImpl() && !e.impl.expired() && e.data == wc.data_ptr() &&
+          e.version == wc._version() && e.t == t && e.k == k && e.n == n && e.stream == stream) {
+        if (i + 1 != cache.size()) std::rotate(cache.begin() + i, cache.begin() + i + 1, cache.end());   // most recent last
+        return cache.back().ws;
+      }
+    }
+  }
+  Tensor ws = torch::empty({std::max<int64_t>(16, gphl_segment_mm_tc_workspace_bytes(t, k, n))}, wc.options().dtype(torch::kUInt8));
+  check_rc(gphl_segment_mm_tc_prepare_weights(wc.data_ptr<float>(), t, k, n, ws.data_ptr(), stream), "gphl_segment_mm_tc_prepare_weights");
+  if (trackable) {
+    cache.erase(std::remove_if(cache.begin(), cache.end(), [](const PreparedWeights &e) { return e.impl.expired(); }), cache.end());
+    if (cache.size() >= 64) cache.erase(cache.begin());
+    cache.push_back(PreparedWeights{c10::weak_intrusive_ptr<c10::TensorImpl>(wc.getIntrusivePtr()), wc.data_ptr(), wc._version(),
+                                    t, k, n, stream, ws});
+  }
+  return ws;
+}
+
 Tensor segment_mm(const Tensor &x, const Tensor &w, const c10::optional<Tensor> &pointer, int64_t n_types, int64_t rows,
                   const c10::optional<Tensor> &gather, const char *what) {
   TORCH_CHECK(pointer.has_value(), what, " needs the type pointer (SetNtypePointer / SetEtypePointer)");
@@ -457,13 +497,12 @@ Tensor segment_mm(const Tensor &x, const Tensor &w, const c10::optional<Tensor> 
   const bool tc = (k % 4 == 0) && !(k <= 64 && n <= 32) && (reinterpret_cast<uintptr_t>(xc.data_ptr()) % 16 == 0) &&
                   (reinterpret_cast<uintptr_t>(y.data_ptr()) % 16 == 0);
   if (tc) {
-    // tensor-core path: the split weights live in a scratch tensor from the caching allocator
-    Tensor ws = torch::empty({std::max<int64_t>(16, gphl_segment_mm_tc_workspace_bytes(n_types, k, n))},
-                             xc.options().dtype(torch::kUInt8));
-    check_rc(gphl_segment_mm_tc_f32(xc.data_ptr<float>(), wc.data_ptr<float>(), pc.data_ptr<int32_t>(), n_types, rows, k, n,
-                                    gather.has_value() ? gi.data_ptr<int64_t>() : nullptr, nullptr, 0, ws.data_ptr(),
-                                    y.data_ptr<float>(), stream_of(xc)),
-             "gphl_segment_mm_tc_f32");
+    // tensor-core path: the split, transposed weights depend on the weight tensor alone and are kept per tensor
+    Tensor ws = prepared_weights(wc, n_types, k, n, stream_of(xc));
+    check_rc(gphl_segment_mm_tc_prepared_f32(xc.data_ptr<float>(), ws.data_ptr(), pc.data_ptr<int32_t>(), n_types, rows, k, n,
+                                             gather.has_value() ? gi.data_ptr<int64_t>() : nullptr, nullptr, 0,
+                                             y.data_ptr<float>(), stream_of(xc)),
+             "gphl_segment_mm_tc_prepared_f32");
   } else {
     check_rc(gphl_segment_mm_f32(xc.data_ptr<float>(), wc.data_ptr<float>(), pc.data_ptr<int32_t>(), n_types, rows, k, n,
                                  gather.has_value() ? gi.data_ptr<int64_t>() : nullptr, y.data_ptr<float>(),

@@ -165,6 +165,20 @@ class ShardedLayer:
                                group=self.group)
         self.send_rows = asked                                                    # rows of my block, grouped by requester
         self.shard.node_indices = torch.searchsorted(keys, owner_of[idx64] * n + idx64).to(torch.int32)
+        # the destination rows of this shard, requested from their owners the same way (the GAT layer needs the
+        # destination-side attention score of its own rows, which their owners compute): grouped by owner, then by id
+        dst_ids = torch.arange(self.shard.row0, self.shard.row1, dtype=torch.int64, device=dev)
+        dkeys, dperm = torch.sort(owner_of[dst_ids] * n + dst_ids)
+        dst_sorted = dst_ids[dperm]
+        self.dst_recv_counts = torch.bincount(owner_of[dst_sorted], minlength=world).tolist()
+        dsend = torch.empty(world, dtype=torch.int64, device=dev)
+        dist.all_to_all_single(dsend, torch.tensor(self.dst_recv_counts, dtype=torch.int64, device=dev), group=self.group)
+        self.dst_send_counts = dsend.tolist()
+        dasked = torch.empty(int(sum(self.dst_send_counts)), dtype=torch.int64, device=dev)
+        dist.all_to_all_single(dasked, local_of[dst_sorted].contiguous(), output_split_sizes=self.dst_send_counts,
+                               input_split_sizes=self.dst_recv_counts, group=self.group)
+        self.dst_send_rows = dasked
+        self.dst_position = torch.searchsorted(dkeys, owner_of[dst_ids] * n + dst_ids)     # received order -> row order
         self.proj = torch.zeros((c0, feat), dtype=dtype, device=dev)               # my projected rows
         self.send_buf = torch.empty((asked.numel(), feat), dtype=dtype, device=dev)
         self.gathered = torch.empty((needed.numel(), feat), dtype=dtype, device=dev)   # compact: only the rows this shard reads
@@ -201,6 +215,24 @@ class ShardedLayer:
         except Exception as ex:  # noqa: BLE001 - any failure means "use the all-to-all"
             self.push = False
             self.push_unavailable = repr(ex)[:300]
+
+    def exchange_rows(self, owned: torch.Tensor, which: str = "sources") -> torch.Tensor:
+        """All-to-all of rows of a (num_owned, width) tensor this rank computed: ``which="sources"`` returns the rows
+        this shard reads, in the compact order its renumbered indices refer to; ``which="destinations"`` returns the
+        rows of this shard's own destination range, in row order.  Halo exchanges only."""
+        assert self.exchange == "halo"
+        if which == "sources":
+            rows, sc, rc = self.send_rows, self.send_counts, self.recv_counts
+        else:
+            rows, sc, rc = self.dst_send_rows, self.dst_send_counts, self.dst_recv_counts
+        if owned.is_cuda:
+            from . import capi
+            packed = capi.gather_rows(rows, owned)
+        else:
+            packed = owned.index_select(0, rows)
+        got = torch.empty((int(sum(rc)),) + tuple(owned.shape[1:]), dtype=owned.dtype, device=owned.device)
+        dist.all_to_all_single(got, packed, output_split_sizes=rc, input_split_sizes=sc, group=self.group)
+        return got if which == "sources" else got.index_select(0, self.dst_position)
 
     @property
     def block_range(self):
@@ -345,8 +377,35 @@ def gat_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, fc_weight, 
     """One GAT layer on this rank: project the local source block (z, el, er), all-gather the three, then run the
     fused attention operator over the local destination rows.  er is needed for the local *destination* rows, whose
     edge-balanced range differs from the equal source block, so it is gathered too (N x H floats)."""
+    if sl.exchange == "halo":
+        # sparse form: every rank projects the rows it owns and computes their two attention scores; the rows this
+        # shard reads travel as in the GCN layer (z through project_and_gather, which may store them straight into the
+        # receivers' buffers; the 8-float score rows through a small all-to-all), and the destination-side scores of
+        # this shard's own rows come from their owners the same way
+        heads, dim = attn_src.shape
+        scores = {}
+
+        def fill(r0, r1, out):
+            if feature_block.is_cuda:
+                from . import capi
+                from .layers import project
+                z = project(feature_block[r0:r1], fc_weight, out=out)
+                scores["el"], scores["er"] = capi.gat_head_scores(z, attn_src.contiguous(), attn_dst.contiguous())
+            else:
+                z = torch.mm(feature_block[r0:r1], fc_weight)
+                zv = z.view(-1, heads, dim)
+                scores["el"], scores["er"] = (zv * attn_src).sum(-1), (zv * attn_dst).sum(-1)
+                out.copy_(z)
+
+        full_z = sl.project_and_gather(fill)
+        full_el = sl.exchange_rows(scores["el"], "sources")
+        er_local = sl.exchange_rows(scores["er"], "destinations")
+        if aggregate is None:
+            from . import capi
+            return capi.gat_fused(sl.shard.pointer, sl.shard.node_indices, None, full_el, er_local, full_z, slope, sl.plan)
+        return aggregate(sl.shard, full_el, er_local, full_z)
     assert sl.chunks == 1 and sl.exchange == "allgather", \
-        "the GAT layer gathers three tensors in one step: build its ShardedLayer with chunks=1, exchange='allgather'"
+        "the dense GAT layer gathers three tensors in one step: build its ShardedLayer with chunks=1"
     lo, hi = sl.block_range
     heads, dim = attn_src.shape
     mine = sl.my_block()

@@ -26,12 +26,13 @@ import torch
 from . import layers, synthetic
 
 
-def check_equal(first, second, rtol: float = 1e-3) -> bool:
-    """Same contract as the reference's (python/graphiler/utils/bench.py:10-16): skipped when either run hit OOM."""
+def check_equal(first, second, rtol: float = 1e-3, atol: float = 0.0) -> bool:
+    """Same contract as the reference's (python/graphiler/utils/bench.py:10-16): skipped when either run hit OOM.
+    ``atol`` (the reference has none: its inputs are all positive) admits sums of signed terms that cancel to ~0."""
     if first is None or second is None:
         print("cannot guarantee correctness because of OOM")
         return False
-    np.testing.assert_allclose(first.detach().cpu().numpy(), second.detach().cpu().numpy(), rtol=rtol)
+    np.testing.assert_allclose(first.detach().cpu().numpy(), second.detach().cpu().numpy(), rtol=rtol, atol=atol)
     print("correctness check passed!")
     return True
 
@@ -50,6 +51,12 @@ def empty_cache(func: Callable) -> Callable:
 
 
 def _timed(fn: Callable, repeat: int) -> float:
+    if not torch.cuda.is_available():                      # host-only runs (the compiled series on a CPU registration)
+        import time
+        t0 = time.perf_counter()
+        for _ in range(repeat):
+            fn()
+        return (time.perf_counter() - t0) * 1e3 / repeat
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     start.record()
@@ -82,9 +89,12 @@ def bench(net: Callable, net_params: Sequence, tag: str = "", nvprof: bool = Fal
     try:
         for _ in range(5):
             out = net(*net_params)
-        torch.cuda.synchronize()
-        offset = torch.cuda.memory_allocated()
-        torch.cuda.reset_peak_memory_stats()
+        on_gpu = torch.cuda.is_available()
+        if on_gpu:
+            torch.cuda.synchronize()
+            offset = torch.cuda.memory_allocated()
+            torch.cuda.reset_peak_memory_stats()
+        memory = memory and on_gpu
         if nvprof:
             torch.cuda.profiler.start()
         elapsed = _timed(lambda: net(*net_params), repeat)
@@ -110,9 +120,10 @@ def bench(net: Callable, net_params: Sequence, tag: str = "", nvprof: bool = Fal
     return out
 
 
-def model(name: str, config: str, device: str = "cuda:0", scale: float = 1.0):
+def model(name: str, config: str, device: str = "cuda:0", scale: float = 1.0, single_layer: bool = False):
     """(network, parameters) of one example model on one synthetic configuration: a callable running the model's
-    layers through this library and the tuple of tensors it takes."""
+    layers through this library and the tuple of tensors it takes.  ``single_layer`` keeps only the first layer of
+    the two-layer models (what one ``update_all`` of the compiled series computes)."""
     gen_dev = device if config == "c5" else "cpu"
     wl = synthetic.make(config, scale=scale, device=gen_dev).to(device)
     pg = layers.PreparedGraph(wl.graph)
@@ -120,6 +131,8 @@ def model(name: str, config: str, device: str = "cuda:0", scale: float = 1.0):
     if name == "gcn":
         nrm = layers.gcn_norms(pg)
         ws = [p[k] for k in ("w1", "w2") if k in p] or [p["gcn_w"]]
+        if single_layer:
+            ws = ws[:1]
 
         def net(x):
             for i, w in enumerate(ws):
@@ -132,11 +145,12 @@ def model(name: str, config: str, device: str = "cuda:0", scale: float = 1.0):
         norm = wl.edata["norm"]
 
         def net(x):
-            return layers.rgcn_layer(pg, layers.rgcn_layer(pg, x, p["w1"], norm), p["w2"], norm)
+            h = layers.rgcn_layer(pg, x, p["w1"], norm)
+            return h if single_layer else layers.rgcn_layer(pg, h, p["w2"], norm)
     elif name == "hgt":
         def net(x):
             h = layers.hgt_layer(pg, x, p, int(hy["heads"]), hy["sqrt_dk"])
-            return layers.hgt_layer(pg, h, p, int(hy["heads"]), hy["sqrt_dk"])
+            return h if single_layer else layers.hgt_layer(pg, h, p, int(hy["heads"]), hy["sqrt_dk"])
     else:
         raise ValueError(f"unknown model {name}")
     return net, (wl.feats,)
@@ -158,7 +172,7 @@ DEFAULT_CONFIG: Dict[str, str] = {"gat": "c1", "gcn": "c2", "rgcn": "c3", "hgt":
 COMPILED_TAGS = ["1+compile", "2+reorder", "3+fusion", "4+extra-fusion", "5-layers"]
 
 
-def load_reference_wrapper(graphiler_path: Optional[str], home: Optional[str] = None):
+def load_reference_wrapper(graphiler_path: Optional[str], home: Optional[str] = None, ops_lib: Optional[str] = None):
     """Make the reference's ``graphiler`` package importable and point it at this operator library: HOME becomes a
     scratch directory (or ``home``) whose .dgl/ holds copies of libgraphiler.so and libgphl.so."""
     import os
@@ -170,8 +184,11 @@ def load_reference_wrapper(graphiler_path: Optional[str], home: Optional[str] = 
     os.environ["HOME"] = home
     dgl = os.path.join(home, ".dgl")
     os.makedirs(dgl, exist_ok=True)
-    for lib in (capi.TORCH_OPS_LIB, capi.KERNEL_LIB):
-        shutil.copy(str(lib), os.path.join(dgl, os.path.basename(str(lib))))
+    if ops_lib:                                            # another registration of the same operators (tests)
+        shutil.copy(str(ops_lib), os.path.join(dgl, "libgraphiler.so"))
+    else:
+        for lib in (capi.TORCH_OPS_LIB, capi.KERNEL_LIB):
+            shutil.copy(str(lib), os.path.join(dgl, os.path.basename(str(lib))))
     if graphiler_path:
         sys.path.insert(0, graphiler_path)
     import contextlib
@@ -182,13 +199,13 @@ def load_reference_wrapper(graphiler_path: Optional[str], home: Optional[str] = 
 
 
 def compiled_series(name: str, config: str, graphiler_path: Optional[str] = None, device: str = "cuda:0",
-                    scale: float = 1.0, repeat: int = 50, memory: bool = True) -> pd.Series:
+                    scale: float = 1.0, repeat: int = 50, memory: bool = True, ops_lib: Optional[str] = None) -> pd.Series:
     """Time one example model through the reference's compiler at every optimisation step (see above) and through
     ``layers.py`` directly; returns the (tag, metric) series the reference's breakdown() returns."""
     import contextlib
     import io
     from types import SimpleNamespace
-    graphiler = load_reference_wrapper(graphiler_path)
+    graphiler = load_reference_wrapper(graphiler_path, ops_lib=ops_lib)
     from . import compiled_udfs as udf
     from .fusion import extra_fusion
     gen_dev = device if config == "c5" else "cpu"
@@ -218,7 +235,8 @@ def compiled_series(name: str, config: str, graphiler_path: Optional[str] = None
         funcs = (udf.hgt_message, udf.hgt_reduce, udf.hgt_update)
         ndata = {"h": wl.feats}
         ntd = {k: p[k] for k in ("k_weight", "v_weight", "q_weight", "a_weight", "skip")}
-        etd = {k: p[k] for k in ("relation_att", "relation_msg", "relation_pri")}
+        etd = {k: p[k] for k in ("relation_att", "relation_msg")}
+        etd["relation_pri"] = p["relation_pri"][:, :1].contiguous()       # one head: one prior per relation
         msg_params = (float(hy["sqrt_dk"]),)
     else:
         raise ValueError(f"unknown model {name}")
@@ -239,12 +257,13 @@ def compiled_series(name: str, config: str, graphiler_path: Optional[str] = None
                 if extra:
                     extra_fusion(mpdfg)
             outs[tag] = bench(run, (mpdfg,), tag=tag, memory=memory, repeat=repeat, log=log)
-        net, params = model(name, config, device=device, scale=scale)
-        bench(net, params, tag="5-layers", memory=memory, repeat=repeat, log=log)
+        if str(device).startswith("cuda"):
+            net, params = model(name, config, device=device, scale=scale, single_layer=True)
+            bench(net, params, tag="5-layers", memory=memory, repeat=repeat, log=log)
     base = outs.get("3+fusion")
     for tag, out in outs.items():
         if out is not None and base is not None and tag != "3+fusion":
-            check_equal(out, base, rtol=1e-3)
+            check_equal(out, base, rtol=1e-3, atol=1e-5)
     return log
 
 
@@ -259,13 +278,16 @@ def main():
     ap.add_argument("--nvprof", action="store_true", help="bracket the timed calls with cudaProfilerStart/Stop")
     ap.add_argument("--compiled", action="store_true",
                     help="time the model through the reference's mpdfg_builder + update_all at every optimisation step")
+    ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--ops-lib", default=None, help="--compiled: another operator library to install (tests)")
     ap.add_argument("--graphiler-path", default=None,
                     help="directory that holds the reference's `graphiler` Python package (default: already importable)")
     a = ap.parse_args()
     config = a.config or DEFAULT_CONFIG[a.model]
     tag = f"{a.model}-{config}"
     if a.compiled:
-        log = compiled_series(a.model, config, a.graphiler_path, scale=a.scale, repeat=a.repeat, memory=True)
+        log = compiled_series(a.model, config, a.graphiler_path, device=a.device, scale=a.scale, repeat=a.repeat, memory=True,
+                              ops_lib=a.ops_lib)
         print(json.dumps({"model": a.model, "config": config, "scale": a.scale,
                           **{t: {"time_ms": float(log.at[(t, "time")]), "mem_mb": float(log.at[(t, "mem")])}
                              for t in COMPILED_TAGS}}))

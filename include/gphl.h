@@ -109,6 +109,28 @@ int gphl_spmm_u_mul_e_sum_f32(const gphl_plan *plan, const int32_t *pointer, con
                               const int32_t *edge_idx, int64_t n_rows, int64_t heads, int64_t dim,
                               const float *x, const float *w, float *y, void *stream);
 
+/* ---- general g-SpMM --------------------------------------------------------------------
+ * SpMMCsrKernel with its functors and broadcast offsets (spmm.cuh:30-123, functor.cuh:18-213, bcast.h:21-35,
+ * bcast.cc:20-77), which no registered operator of the reference reaches:
+ *   out[v,j] = reduce_{i in row v} op(u[node_idx[i], u_off[j]], e[edge_idx[i], e_off[j]])
+ * op: add, sub, mul, div, copy_lhs (u only), copy_rhs (e only), evaluated in fp32 as written; reduce: sum (terms
+ * accumulated in double, rounded once), max, min (bit-exact; ties keep the first position; an empty row yields
+ * -inf / +inf and argument 0, as the reference's kernel does).  arg_u / arg_e (n_rows x out_len int32, optional):
+ * the neighbour id / edge id behind every max or min.  u_off / e_off: one int64 column offset per output column, or
+ * both NULL when u and e already have out_len columns.  edge_idx NULL: edge id == position. */
+#define GPHL_OP_ADD 0
+#define GPHL_OP_SUB 1
+#define GPHL_OP_MUL 2
+#define GPHL_OP_DIV 3
+#define GPHL_OP_COPY_LHS 4
+#define GPHL_OP_COPY_RHS 5
+#define GPHL_REDUCE_SUM 0
+#define GPHL_REDUCE_MAX 1
+#define GPHL_REDUCE_MIN 2
+int gphl_gspmm_f32(int32_t op, int32_t reduce, const int32_t *pointer, const int32_t *node_idx, const int32_t *edge_idx,
+                   int64_t n_rows, int64_t out_len, const float *u, int64_t u_len, const float *e, int64_t e_len,
+                   const int64_t *u_off, const int64_t *e_off, float *out, int32_t *arg_u, int32_t *arg_e, void *stream);
+
 /* ---- SDDMM: z[e,:] = l[src[e],:] + r[dst[e],:] ----------------------------------------
  * my_ops::gsddmm_u_add_v_mul_alpha (sddmm.cu:118-134; kernel SDDMMCooKernel,
  * sddmm.cuh:34-71; `alpha` is ignored there and has no counterpart here).  COO arrays in
@@ -224,6 +246,14 @@ int64_t gphl_segment_mm_tc_workspace_bytes(int64_t n_types, int64_t k, int64_t n
 int gphl_segment_mm_tc_f32(const float *x, const float *w, const int32_t *type_pointer, int64_t n_types,
                            int64_t m, int64_t k, int64_t n, const int64_t *gather_idx,
                            const float *row_scale, int32_t relu, void *workspace, float *y, void *stream);
+/* The same in two steps, for weights that are constants of a layer: prepare_weights splits and transposes w into
+ * `workspace` once; prepared_f32 multiplies with a workspace prepared earlier (for the same n_types, k, n) and
+ * launches the tensor-core kernel only.  The kernel receives the weight slabs by TMA (cp.async.bulk.tensor, 128-byte
+ * swizzle) from a tensor map over `workspace`, which must lie in the launching GPU's own memory. */
+int gphl_segment_mm_tc_prepare_weights(const float *w, int64_t n_types, int64_t k, int64_t n, void *workspace, void *stream);
+int gphl_segment_mm_tc_prepared_f32(const float *x, const void *workspace, const int32_t *type_pointer, int64_t n_types,
+                                    int64_t m, int64_t k, int64_t n, const int64_t *gather_idx, const float *row_scale,
+                                    int32_t relu, float *y, void *stream);
 /* Barrier waits that ran out inside tensor-core kernels since the library was loaded (0 in a
  * healthy process; each kernel wait is bounded and a block that gives up frees its tensor memory
  * and returns).  Synchronises the device. */

@@ -132,6 +132,46 @@ def dst_mul_e_sum(x, w, out_pointer, out_node_indices, out_edge_indices):
 
 # ---- SDDMM family (src/ops/dgl_primitives/sddmm.cu:118-129, sddmm.cuh:34-120) -----------
 
+def gspmm(op, reduce, pointer, node_indices, edge_indices, u=None, e=None):
+    """General g-SpMM, literal loops (small inputs): SpMMCsrKernel with its functors (src/ops/dgl_primitives/
+    spmm.cuh:30-75, functor.cuh:18-213) and numpy broadcasting of the trailing dimensions (bcast.cc:20-77).
+    The binary operator is evaluated in float32 as the reference does; sums are returned in float64 (truth for a
+    tolerance check), max / min in float32 (bit-exact), with the arguments of the first extreme position; an empty
+    row gives -inf / +inf and argument 0.  Returns (out, arg_u, arg_e)."""
+    ptr, nid, eid = _np(pointer, np.int64), _np(node_indices, np.int64), _np(edge_indices, np.int64)
+    uu = None if u is None else _np(u, np.float32)
+    ee = None if e is None else _np(e, np.float32)
+    f = {"add": np.add, "sub": np.subtract, "mul": np.multiply, "div": np.divide,
+         "copy_lhs": lambda a, b: a, "copy_rhs": lambda a, b: b}[op]
+    n = ptr.shape[0] - 1
+    if op == "copy_lhs":
+        trailing = uu.shape[1:]
+    elif op == "copy_rhs":
+        trailing = ee.shape[1:]
+    else:
+        trailing = np.broadcast_shapes(uu.shape[1:], ee.shape[1:])
+    out = np.zeros((n,) + tuple(trailing), dtype=np.float64 if reduce == "sum" else np.float32)
+    au, ae = np.zeros(out.shape, dtype=np.int32), np.zeros(out.shape, dtype=np.int32)
+    if reduce != "sum":
+        out[...] = -np.inf if reduce == "max" else np.inf
+    with np.errstate(divide="ignore", invalid="ignore"):
+        for v in range(n):
+            for i in range(ptr[v], ptr[v + 1]):
+                a = None if uu is None else uu[nid[i]]
+                b = None if ee is None else ee[eid[i]]
+                val = np.broadcast_to(np.asarray(f(a, b), dtype=np.float32), trailing)
+                if reduce == "sum":
+                    out[v] += val.astype(np.float64)
+                else:
+                    better = out[v] < val if reduce == "max" else out[v] > val
+                    out[v] = np.where(better, val, out[v])
+                    if op != "copy_rhs":                      # arguments only for the operands the operator reads
+                        au[v] = np.where(better, nid[i], au[v])
+                    if op != "copy_lhs":
+                        ae[v] = np.where(better, eid[i], ae[v])
+    return out, au, ae
+
+
 def sddmm_u_add_v(lhs, rhs, COO_src, COO_dst):
     """z[e] = lhs[COO_src[e]] + rhs[COO_dst[e]]; the ``alpha`` argument of the registered
     operator is ignored by the reference (sddmm.cu:116-129)."""

@@ -1,5 +1,7 @@
-"""One pass over the gather operators with the accumulator kind forced by GPHL_ACC (read once per process, hence a
-script for a child process):  GPHL_ACC=twosum|f64|mixed python tests/acc_kinds_case.py   -> prints OK or raises."""
+"""One pass over the gather operators with the accumulator kind forced by GPHL_ACC (1 two-sum fp32, 2 double,
+3 alternating), through the measurement build of the kernel library (lib/libgphl_measure.so: the product library
+compiles the choice in), also over the column-sliced kernels (GPHL_SLICE_LPR).  A script for a child process:
+    GPHL_ACC=1|2|3 [GPHL_SLICE_LPR=8|16|32] python tests/acc_kinds_case.py   -> prints OK or raises."""
 import sys
 from pathlib import Path
 
@@ -11,6 +13,7 @@ import torch  # noqa: E402
 from graphiler_b200 import capi, synthetic  # noqa: E402
 from oracle import ops_oracle as O  # noqa: E402
 
+capi.load_library(Path(capi.KERNEL_LIB).with_name("libgphl_measure.so"), make_default=True)
 DEV = "cuda:0"
 wl = synthetic.make_c5(scale=0.002)
 g, gd = wl.graph, wl.graph.to(DEV)

@@ -58,13 +58,21 @@ def _worker(rank, world, port, tmp):
     yg = gd.gat_layer_sharded(sg, x[lo:hi].contiguous(), p["fc_weight"], p["attn_src"], p["attn_dst"], 0.2)
     full_gat = sg.gather_outputs(yg)
     single_gat = layers.gat_layer(pg, x, p["fc_weight"], p["attn_src"], p["attn_dst"], 0.2)
+    # GAT over the sparse exchange (all-to-all, then peer stores for the z rows)
+    gat_sparse_ok = True
+    for ex in ("halo", "push"):
+        sgh = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, p["fc_weight"].shape[1], rank=rank, world=world,
+                              exchange=ex)
+        for _ in range(2):
+            ygh = gd.gat_layer_sharded(sgh, x[sgh.owned_rows].contiguous(), p["fc_weight"], p["attn_src"], p["attn_dst"], 0.2)
+            gat_sparse_ok = gat_sparse_ok and bool(torch.equal(sgh.gather_outputs(ygh), single_gat))
     torch.cuda.synchronize()
     if rank == 0:
         # the dense projections run on different row blocks but every row's dot products are computed identically,
         # and the sparse kernels do not depend on the sharding: bit-exact
         np.save(tmp + "/ok.npy", np.array([bool(torch.equal(full, single)), full.shape[0] == g.num_nodes,
                                             bool(torch.equal(full_gat, single_gat)), bool(torch.equal(full4, single)),
-                                            bool(torch.equal(fullh, single)), pushed_ok]))
+                                            bool(torch.equal(fullh, single)), pushed_ok, gat_sparse_ok]))
     dist.barrier()
     dist.destroy_process_group()
 

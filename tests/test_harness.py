@@ -34,3 +34,42 @@ def test_models_run_timed_and_replayed_from_a_cuda_graph(name, config, scale):
     assert log.at[(tag, "time")] > 0 and log.at[(tag, "time_cuda_graph")] > 0 and log.at[(tag, "mem")] >= 0
     replay_out = net(*params)
     assert torch.equal(out, replay_out)                         # deterministic from call to call
+
+
+def _compiled(model, device, scale, extra=()):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    ref = root / "oracle" / "_ref"
+    if not (ref / "graphiler").exists():
+        pytest.skip("the reference's compiler was not built here (oracle/build_ref.py needs its source tree once)")
+    cmd = [sys.executable, "-m", "graphiler_b200.harness", "--model", model, "--compiled", "--graphiler-path", str(ref),
+           "--device", device, "--scale", str(scale), "--repeat", "2", *extra]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=str(root))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("correctness check passed!") == 3, r.stdout[-2000:]
+    return json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+
+
+@pytest.mark.parametrize("model,scale", [("gcn", 0.02), ("gat", 0.02), ("rgcn", 0.02), ("hgt", 0.004)])
+def test_series_through_the_reference_compiler_on_the_cpu_registration(model, scale):
+    """`--compiled`: the model's user-defined functions built by the reference's mpdfg_builder at its three
+    optimisation levels plus this package's fusion patterns, run by its update_all; here against the CPU
+    registration of the operators (one process per model: the reference's builder keeps static state)."""
+    from pathlib import Path
+    cpu_lib = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libgraphiler_cpu.so"
+    if not cpu_lib.exists():
+        pytest.skip("oracle/_ref/libgraphiler_cpu.so was not built")
+    rep = _compiled(model, "cpu", scale, ("--ops-lib", str(cpu_lib)))
+    for tag in ("1+compile", "2+reorder", "3+fusion", "4+extra-fusion"):
+        assert rep[tag]["time_ms"] > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("model,scale", [("gcn", 0.05), ("gat", 0.2), ("rgcn", 0.05), ("hgt", 0.02)])
+def test_series_through_the_reference_compiler_on_the_gpu(model, scale):
+    rep = _compiled(model, "cuda:0", scale)
+    for tag in harness.COMPILED_TAGS:
+        assert rep[tag]["time_ms"] > 0

@@ -96,35 +96,6 @@ def test_spmm_fast_accumulation_is_plain_fp32(graph, feat):
     assert (err <= 1e-6 * (1 + mag)).all()
 
 
-def test_spmm_bulk_async_staged_variant_matches_default():
-    """GPHL_GATHER=bulk selects the cp.async.bulk + mbarrier staged kernel for rows >= 512 B (read once per process, so
-    the check runs in a child process): same bits as the default vector-load kernel."""
-    import os
-    import subprocess
-    import sys
-    code = (
-        "import torch, sys; sys.path.insert(0, '.');"
-        "from graphiler_b200 import capi, synthetic;"
-        "wl = synthetic.make_c5(scale=0.003); g = wl.graph.to('cuda:0');"
-        "out = {};"
-        "\nfor f, dt in ((256, torch.float32), (128, torch.float32), (256, torch.bfloat16), (512, torch.float32)):"
-        "\n    x = torch.randn(g.num_nodes, f, generator=torch.Generator().manual_seed(f)).to(dt).to('cuda:0')"
-        "\n    plan = capi.Plan(g.in_pointer, f, chunk=64)"
-        "\n    y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan, relu=True)"
-        "\n    out[f'{f}_{dt}'] = y.cpu()"
-        "\ntorch.save(out, sys.argv[1])")
-    import tempfile
-    with tempfile.TemporaryDirectory() as d:
-        paths = {}
-        for mode in ("ldg", "bulk"):
-            paths[mode] = os.path.join(d, mode + ".pt")
-            env = dict(os.environ, GPHL_GATHER=mode)
-            subprocess.run([sys.executable, "-c", code, paths[mode]], check=True, env=env, cwd=str(ROOT), timeout=600)
-        a, b = torch.load(paths["ldg"]), torch.load(paths["bulk"])
-        assert a.keys() == b.keys() and len(a) == 4
-        for k in a:
-            assert torch.equal(a[k], b[k]), k
-
 
 @pytest.mark.parametrize("feat", [16, 128])
 def test_spmm_copy_e_sum(graph, feat):
@@ -197,9 +168,11 @@ def test_sddmm_u_dot_v_row_order(graph, heads, dim, with_plan):
     f = heads * dim
     l = torch.randn(g.num_nodes, f, device=DEV)
     r = torch.randn(g.num_nodes, f, device=DEV)
-    plan = capi.Plan(g.in_pointer, f, chunk=8) if with_plan else None          # chunk 8: rows cut into pieces
+    plan = capi.Plan(g.in_pointer, f, chunk=32) if with_plan else None         # chunk 32: rows cut into pieces
     z = capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_node_indices, g.in_edge_indices, l, r, heads, plan)
     close(z, O.sddmm_u_dot_v(l, r, graph.COO_src, graph.COO_dst, heads))
+    if g.num_edges == 0:
+        return
     le = torch.randn(g.num_edges, f, device=DEV)
     z = capi.sddmm_u_dot_v_csc(g.in_pointer, g.in_edge_indices, g.in_edge_indices, le, r, heads, plan)
     truth = O.sddmm_u_dot_v(le, r, torch.arange(graph.num_edges), graph.COO_dst, heads)
@@ -365,14 +338,19 @@ def test_ops_on_config_shaped_graphs(name, scale):
     close(a, O.segment_softmax(w.cpu() * 5, graph.in_pointer, graph.in_edge_indices))
 
 
-@pytest.mark.parametrize("kind", ["twosum", "f64", "mixed"])
-def test_gather_accumulator_kinds(kind):
+@pytest.mark.parametrize("kind,slice_lanes", [("1", ""), ("2", ""), ("3", ""), ("3", "16"), ("3", "32"), ("2", "8")])
+def test_gather_accumulator_kinds(kind, slice_lanes):
     """The three exact accumulators of the gather kernels (compensated fp32, double, half of the column pairs each)
-    meet the same tolerance; the library picks one per operator, GPHL_ACC forces one for the whole process."""
+    meet the same tolerance, in the general kernel and in the column-sliced pair; the product library picks one per
+    operator, the measurement build takes the choice from the environment."""
     import os
     import subprocess
     import sys
+    from graphiler_b200 import build
+    build.build_kernels(measure=True)
     env = dict(os.environ, GPHL_ACC=kind)
+    if slice_lanes:
+        env["GPHL_SLICE_LPR"] = slice_lanes
     r = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "acc_kinds_case.py")], env=env,
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and r.stdout.strip().endswith("OK"), r.stdout[-2000:] + r.stderr[-2000:]
@@ -401,3 +379,77 @@ def test_argument_errors_are_reported_not_fatal():
         capi.Plan(g.in_pointer, 8, chunk=33)
     y = capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, plan)           # context still healthy
     close(y, O.spmm_src(x, g.in_pointer.cpu(), g.in_node_indices.cpu()))
+
+
+def test_segment_mm_split_weights_are_cached_per_tensor_version():
+    """The tensor-core path keeps the split copy of a weight tensor between calls; an in-place update of the weights
+    (a new version of the same tensor) must be seen by the next call, and a view passed by `linear` must hit the
+    entry of the tensor it views."""
+    m, k, n = 300, 64, 48
+    x = torch.randn(m, k, device=DEV)
+    w = torch.randn(2, k, n, device=DEV) * 0.2
+    ptr = torch.tensor([0, 120, m], dtype=torch.int32, device=DEV)
+    y1 = capi.segment_mm(x, w, ptr, tensor_cores=True)
+    y2 = capi.segment_mm(x, w, ptr, tensor_cores=True)                      # served from the cached split
+    assert torch.equal(y1, y2)
+    w.mul_(2.0)                                                             # exact in floating point
+    y3 = capi.segment_mm(x, w, ptr, tensor_cores=True)
+    assert torch.equal(y3, y1 * 2.0)
+    wd = torch.randn(k, n, device=DEV) * 0.2
+    d1 = capi.linear(x, wd)
+    wd.add_(1.0)
+    d2 = capi.linear(x, wd)
+    truth = x.double().cpu().numpy() @ wd.double().cpu().numpy()
+    mag = np.abs(x.double().cpu().numpy()) @ np.abs(wd.double().cpu().numpy())
+    err = np.abs(d2.cpu().numpy() - truth)
+    assert (err <= 1e-6 + 1e-5 * np.abs(truth) + 2 * 2.0 ** -23 * mag).all() and not torch.equal(d1, d2)
+    assert capi.tc_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "div", "copy_lhs", "copy_rhs"])
+@pytest.mark.parametrize("reduce", ["sum", "max", "min"])
+def test_general_gspmm(graph, op, reduce):
+    """Every binary operator x reducer of the general g-SpMM against the loop oracle: sums within tolerance of the
+    float64 sum of the float32 terms, max / min bit for bit with the neighbour and edge ids that produced them, with
+    and without broadcasting ((N, H, D) against (E, H, 1)), on the reduce side and on the message side."""
+    g = graph.to(DEV)
+    n, e = graph.num_nodes, graph.num_edges
+    gen = torch.Generator().manual_seed(17)
+    shapes = [((n, 6), (e, 6)), ((n, 3, 4), (e, 3, 1))]
+    for us, es in shapes:
+        u = torch.randn(*us, generator=gen)
+        ev = torch.randn(*es, generator=gen) + (3.0 if op == "div" else 0.0)      # keep quotients tame
+        for side in ("in", "out"):
+            arrs = ((graph.in_pointer, graph.in_node_indices, graph.in_edge_indices) if side == "in" else
+                    (graph.out_pointer, graph.out_node_indices, graph.out_edge_indices))
+            darrs = ((g.in_pointer, g.in_node_indices, g.in_edge_indices) if side == "in" else
+                     (g.out_pointer, g.out_node_indices, g.out_edge_indices))
+            want, wu, we = O.gspmm(op, reduce, *arrs, u=None if op == "copy_rhs" else u, e=None if op == "copy_lhs" else ev)
+            res = capi.gspmm(op, reduce, *darrs, u=None if op == "copy_rhs" else u.to(DEV),
+                             e=None if op == "copy_lhs" else ev.to(DEV), return_args=True)
+            if reduce == "sum":
+                close(res, want)
+            else:
+                out, au, ae = res
+                assert np.array_equal(out.cpu().numpy(), want)
+                if au is not None:
+                    assert np.array_equal(au.cpu().numpy(), wu)
+                if ae is not None:
+                    assert np.array_equal(ae.cpu().numpy(), we)
+
+
+def test_general_gspmm_agrees_with_the_tuned_kernels_and_rejects_bad_arguments(graph):
+    g = graph.to(DEV)
+    x = torch.randn(g.num_nodes, 16, device=DEV)
+    w = torch.randn(g.num_edges, 1, device=DEV)
+    a = capi.gspmm("mul", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x, e=w)
+    b = capi.spmm_u_mul_e_sum(g.in_pointer, g.in_node_indices, g.in_edge_indices, x, w, capi.Plan(g.in_pointer, 16))
+    assert torch.allclose(a, b, rtol=1e-6, atol=1e-6)
+    a = capi.gspmm("copy_lhs", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x)
+    assert torch.equal(a, capi.spmm_gather_sum(g.in_pointer, g.in_node_indices, x, capi.Plan(g.in_pointer, 16)))
+    with pytest.raises(capi.GphlError):
+        capi.gspmm("pow", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x, e=w)
+    with pytest.raises(capi.GphlError):
+        capi.gspmm("mul", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x)
+    with pytest.raises(capi.GphlError):
+        capi.gspmm("add", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x, e=torch.randn(g.num_edges, 5, device=DEV))

@@ -215,3 +215,44 @@ def test_c_restatement_matches_numpy_oracle():
     xn = rng.standard_normal((hg.num_nodes, 12)).astype(np.float32)
     t = O.segment_mm(xn[hg.COO_src.numpy()], we, hg.etype_pointer)
     assert np.allclose(K.segment_mm_f64(xn, we, hg.etype_pointer, gather=hg.COO_src), t, rtol=1e-12, atol=1e-12)
+
+
+def test_general_gspmm_oracle_and_broadcast_offsets():
+    """The loop oracle of the general g-SpMM reproduces the pinned operators where they overlap (mul / copy with sum),
+    and the broadcast offset tables restate the reference's CalcBcastOff loop (bcast.cc:34-62)."""
+    from graphiler_b200.capi import broadcast_offsets
+    g = random_graph(30, 150, 3, empty_rows=True)
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((g.num_nodes, 2, 3)).astype(np.float32)
+    w = rng.standard_normal((g.num_edges, 2, 1)).astype(np.float32)
+    out, _, _ = O.gspmm("mul", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x, e=w)
+    want = O.u_mul_e_sum(x.reshape(g.num_nodes, 6), w.reshape(g.num_edges, 2), g.in_pointer, g.in_node_indices, g.in_edge_indices)
+    assert np.allclose(out.reshape(g.num_nodes, 6), want, rtol=1e-6, atol=1e-7)
+    out, _, _ = O.gspmm("copy_lhs", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x)
+    assert np.allclose(out.reshape(g.num_nodes, 6), O.spmm_src(x.reshape(g.num_nodes, 6), g.in_pointer, g.in_node_indices))
+    out, au, ae = O.gspmm("copy_rhs", "max", g.in_pointer, g.in_node_indices, g.in_edge_indices, e=w)
+    deg = g.in_degrees().numpy()
+    assert np.isneginf(out[deg == 0]).all() and (au == 0).all()
+    v = int(np.argmax(deg))
+    seg = g.in_edge_indices[g.in_pointer[v]:g.in_pointer[v + 1]].numpy()
+    assert out[v, 0, 0] == w[seg, 0, 0].max() and ae[v, 0, 0] == seg[np.argmax(w[seg, 0, 0])]
+
+    def calc_bcast_off(ls, rs):                      # the reference's loop, trailing shapes only
+        lo, ro, out_len, sl, sr = [0], [0], 1, 1, 1
+        nd = max(len(ls), len(rs))
+        for j in range(nd):
+            dl = ls[len(ls) - 1 - j] if len(ls) - 1 - j >= 0 else 1
+            dr = rs[len(rs) - 1 - j] if len(rs) - 1 - j >= 0 else 1
+            for i in range(1, max(dl, dr)):
+                for k in range(out_len):
+                    lo.append(lo[k] + i * (i < dl) * sl)
+                    ro.append(ro[k] + i * (i < dr) * sr)
+            out_len *= max(dl, dr)
+            sl, sr = sl * dl, sr * dr
+        return lo, ro
+    for ls, rs in (((3, 4), (3, 1)), ((4,), (1,)), ((2, 1, 5), (3, 5)), ((6,), (6,)), ((1, 4), (3, 1))):
+        shape, lo, ro = broadcast_offsets(ls, rs)
+        wl, wr = calc_bcast_off(ls, rs)
+        assert lo.tolist() == wl and ro.tolist() == wr and int(np.prod(shape)) == len(wl)
+    with pytest.raises(Exception):
+        broadcast_offsets((3,), (4,))

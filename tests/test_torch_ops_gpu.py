@@ -190,3 +190,15 @@ def test_first_operator_call_on_a_graph_can_be_captured(ops):
     assert torch.equal(y, ops.SpMMSrc(x, [1], False, None, G2))
     assert torch.equal(z, ops.gspmm_src_mul_e_sum(x, ops.SegmentSoftmax(w, 1, None, G2), [1], False, None, G2))
     close(y, O.spmm_src(x, wl.graph.in_pointer, wl.graph.in_node_indices))
+
+
+def test_typed_linear_sees_in_place_weight_updates(ops):
+    g = typed_random_graph()
+    G = to_obj(g)
+    x = torch.randn(g.num_nodes, 64, device=DEV)
+    w = torch.randn(g.num_ntypes, 64, 48, device=DEV) * 0.2
+    y1 = ops.SegmentMMNode(x, w, G)
+    assert torch.equal(y1, ops.SegmentMMNode(x, w, G))                      # second call: cached split weights
+    w.mul_(2.0)
+    assert torch.equal(ops.SegmentMMNode(x, w, G), y1 * 2.0)
+    close(y1, O.segment_mm(x.cpu(), (w / 2).cpu(), g.ntype_pointer), rtol=1e-5, atol=2e-6)
