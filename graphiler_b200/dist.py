@@ -77,7 +77,7 @@ class ShardedLayer:
 
     def __init__(self, in_pointer, in_node_indices, num_nodes: int, feat: int, dtype=torch.float32,
                  rank: Optional[int] = None, world: Optional[int] = None, group=None, make_plan: bool = True,
-                 chunks: int = 1, exchange: str = "allgather", ownership: Optional[str] = None):
+                 chunks: int = 1, exchange: str = "allgather", ownership: Optional[str] = None, push_chunks: int = 4):
         self.group = group
         self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
@@ -93,6 +93,7 @@ class ShardedLayer:
         # "push" is the halo exchange with the all-to-all replaced by this library's row-gather kernel storing the
         # requested rows straight into the receivers' buffers over NVLink (peer-mapped symmetric memory)
         self.push = exchange == "push" and self.world > 1
+        self.push_chunks = push_chunks
         self.push_unavailable = None
         if exchange == "push":
             exchange = "halo"
@@ -212,6 +213,18 @@ class ShardedLayer:
             for c in self.send_counts:
                 self.send_offsets.append(self.send_offsets[-1] + c)
             self._push_token = torch.zeros(1, dtype=torch.int32, device=dev)
+            # The projection and the stores overlap piece by piece: the owned rows are cut into `push_chunks` ranges;
+            # every requester's list is in ascending row order, so a range of rows is a range of each list.
+            self.push_chunks = max(1, min(int(self.push_chunks), max(1, self.num_owned)))
+            nm = self.num_owned
+            self.push_bounds = [nm * c // self.push_chunks for c in range(self.push_chunks + 1)]
+            cuts = []
+            bvec = torch.tensor(self.push_bounds, dtype=torch.int64, device=dev)
+            for peer in range(world):
+                a, b = self.send_offsets[peer], self.send_offsets[peer + 1]
+                cuts.append((torch.searchsorted(self.send_rows[a:b].contiguous(), bvec) + a).tolist())
+            self.push_cuts = cuts                                    # push_cuts[peer][c]: first list position of piece c
+            self._push_stream = torch.cuda.Stream(device=dev)
         except Exception as ex:  # noqa: BLE001 - any failure means "use the all-to-all"
             self.push = False
             self.push_unavailable = repr(ex)[:300]
@@ -263,30 +276,41 @@ class ShardedLayer:
         [row_lo, row_hi) of this rank's block (block-relative) into ``out``.  Piece by piece: the collective of a
         piece is issued asynchronously right after its rows were produced and overlaps the next piece's ``fill``."""
         n_mine = self.num_owned
+        if self.exchange == "halo" and self.push:
+            # One launch of the row-gather kernel per receiver and piece, the receivers taken in an order that makes
+            # every step of the loop a permutation of the ranks (no receiver is the target of two senders at once);
+            # the stores go through NVLink into the receiver's slot, on a second stream, while the next piece is
+            # projected.  Slots alternate between steps, so a sender that is one step ahead never overwrites rows a
+            # receiver is still aggregating: between two writes to the same slot lies the other slot's barrier, which
+            # a receiver enters only after that aggregation was launched on the same stream.  The barrier is a
+            # one-word NCCL all-reduce: stream-ordered, and it completes on a rank only when every rank's stores of
+            # this step were finished before it.
+            from . import capi
+            self._mark("start")
+            slot, self.push_slot = self.push_slot, 1 - self.push_slot
+            main, side = torch.cuda.current_stream(), self._push_stream
+            for c in range(self.push_chunks):
+                r0, r1 = self.push_bounds[c], self.push_bounds[c + 1]
+                if r1 > r0:
+                    fill(r0, r1, self.proj[r0:r1])
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    for k in range(self.world):
+                        peer = (self.rank + k) % self.world
+                        a, b = self.push_cuts[peer][c], self.push_cuts[peer][c + 1]
+                        if b > a:
+                            o = self.push_offset[peer] + (a - self.send_offsets[peer])
+                            capi.gather_rows(self.send_rows[a:b], self.proj, out=self.peer_bufs[peer][slot, o:o + (b - a)])
+            self._mark("project")
+            main.wait_stream(side)
+            self._mark("pack")
+            dist.all_reduce(self._push_token, group=self.group)
+            self._mark("exchange")
+            return self._symm_local[slot, :self.halo_rows]
         if self.exchange == "halo":
             self._mark("start")
             fill(0, n_mine, self.proj[:n_mine])
             self._mark("project")
-            if self.push:
-                # One launch of the row-gather kernel per receiver, in an order that makes every step of the loop a
-                # permutation of the ranks (no receiver is the target of two senders at once); the stores go through
-                # NVLink into the receiver's slot.  Slots alternate between steps, so a sender that is one step
-                # ahead never overwrites rows a receiver is still aggregating: between two writes to the same slot
-                # lies the other slot's barrier, which a receiver enters only after that aggregation was launched on
-                # the same stream.  The barrier is a one-word NCCL all-reduce: stream-ordered, and it completes on a
-                # rank only when every rank's stores of this step have been issued before it.
-                from . import capi
-                slot, self.push_slot = self.push_slot, 1 - self.push_slot
-                for k in range(self.world):
-                    peer = (self.rank + k) % self.world
-                    a, b = self.send_offsets[peer], self.send_offsets[peer + 1]
-                    if b > a:
-                        o = self.push_offset[peer]
-                        capi.gather_rows(self.send_rows[a:b], self.proj, out=self.peer_bufs[peer][slot, o:o + (b - a)])
-                self._mark("pack")
-                dist.all_reduce(self._push_token, group=self.group)
-                self._mark("exchange")
-                return self._symm_local[slot, :self.halo_rows]
             if self.proj.is_cuda:
                 from . import capi
                 capi.gather_rows(self.send_rows, self.proj, out=self.send_buf)    # pack the requested rows
@@ -383,18 +407,20 @@ def gat_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, fc_weight, 
         # receivers' buffers; the 8-float score rows through a small all-to-all), and the destination-side scores of
         # this shard's own rows come from their owners the same way
         heads, dim = attn_src.shape
-        scores = {}
+        sdt = torch.float32 if feature_block.is_cuda else feature_block.dtype
+        scores = {k: torch.empty((sl.num_owned, heads), dtype=sdt, device=feature_block.device) for k in ("el", "er")}
+        a_s, a_d = attn_src.contiguous(), attn_dst.contiguous()
 
-        def fill(r0, r1, out):
+        def fill(r0, r1, out):                       # called once, or once per piece of the owned rows
             if feature_block.is_cuda:
                 from . import capi
                 from .layers import project
                 z = project(feature_block[r0:r1], fc_weight, out=out)
-                scores["el"], scores["er"] = capi.gat_head_scores(z, attn_src.contiguous(), attn_dst.contiguous())
+                capi.gat_head_scores(z, a_s, a_d, el=scores["el"][r0:r1], er=scores["er"][r0:r1])
             else:
                 z = torch.mm(feature_block[r0:r1], fc_weight)
                 zv = z.view(-1, heads, dim)
-                scores["el"], scores["er"] = (zv * attn_src).sum(-1), (zv * attn_dst).sum(-1)
+                scores["el"][r0:r1], scores["er"][r0:r1] = (zv * attn_src).sum(-1), (zv * attn_dst).sum(-1)
                 out.copy_(z)
 
         full_z = sl.project_and_gather(fill)
