@@ -49,6 +49,7 @@ SIGNATURES = {
     "gphl_sddmm_u_dot_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_segment_mm_tc_prepare_weights": (c_int, [_P, c_int64, c_int64, c_int64, _P, _P]),
     "gphl_segment_mm_tc_prepared_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, c_int32, _P, _P]),
+    "gphl_scatter_rows_peers_i64": (c_int, [_P, c_int32, _P, _P, _P, _P, c_int64, _P, _P]),
     "gphl_gspmm_f32": (c_int, [c_int32, c_int32, _P, _P, _P, c_int64, c_int64, _P, c_int64, _P, c_int64, _P, _P, _P, _P, _P, _P]),
     "gphl_sddmm_u_dot_v_csc_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_segment_softmax_f32": (c_int, [_P, _P, _P, c_int64, c_int64, _P, _P, _P, _P]),
@@ -314,8 +315,9 @@ def gspmm(op: str, reduce: str, pointer, node_idx, edge_idx, u=None, e=None, ret
     ae = torch.zeros(out.shape, dtype=torch.int32, device=dev) if want_args and use_r else None
     with torch.cuda.device(dev):
         _check(lib().gphl_gspmm_f32(GSPMM_OPS[op], GSPMM_REDUCERS[reduce], _ptr(pointer), _ptr(node_idx, pointer),
-                                    _ptr(edge_idx), n_rows, out_len, _ptr(u) if use_l else None, _feat(u) if use_l else 0,
-                                    _ptr(e) if use_r else None, _feat(e) if use_r else 0, _ptr(uoff), _ptr(eoff), _ptr(out),
+                                    _ptr(edge_idx), n_rows, out_len, _ptr(u, pointer) if use_l else None,
+                                    _feat(u) if use_l else 0, _ptr(e, pointer) if use_r else None, _feat(e) if use_r else 0,
+                                    _ptr(uoff), _ptr(eoff), _ptr(out),
                                     _ptr(au), _ptr(ae), _stream(pointer)), "gspmm")
     return (out, au, ae) if return_args and reduce != "sum" else out
 
@@ -408,6 +410,25 @@ def gather_rows(idx, x, idx2=None, out=None):
     with torch.cuda.device(x.device):
         _check(fn(_ptr(idx), _ptr(idx2), n_out, row_bytes, _ptr(x), _ptr(y), _stream(x)), "gather_rows")
     return y
+
+
+def scatter_rows_peers(idx, x, receivers):
+    """One launch that stores rows of ``x`` into several receivers' buffers (which may be peer-mapped memory of other
+    GPUs): ``receivers`` is a list of ``(buffer, first_row_in_buffer, first_position_in_idx, count)``; receiver p gets
+    ``x[idx[first_position + k]]`` at row ``first_row + k`` of its buffer."""
+    _dev(idx, x)
+    assert idx.dtype == torch.int64
+    n = len(receivers)
+    row_bytes = _feat(x) * x.element_size()
+    arr = lambda vals: (c_int64 * n)(*vals)
+    ptrs = (c_void_p * n)(*[b.data_ptr() for b, _, _, _ in receivers])
+    for b, _, _, _ in receivers:
+        if b.dtype != x.dtype or _feat(b) != _feat(x) or not b.is_contiguous():
+            raise GphlError("scatter_rows_peers: receiver buffers must be contiguous, of x's dtype and row width")
+    with torch.cuda.device(x.device):
+        _check(lib().gphl_scatter_rows_peers_i64(_ptr(idx), n, arr([r[2] for r in receivers]), arr([r[3] for r in receivers]),
+                                                 ptrs, arr([r[1] for r in receivers]), row_bytes, _ptr(x), _stream(x)),
+               "scatter_rows_peers")
 
 
 def segment_mm(x, w, type_pointer, gather_idx=None, out=None, row_scale=None, relu: bool = False,

@@ -10,16 +10,22 @@
 
 namespace gphl {
 
+// `lanes` = min(FV, 256) threads share one edge; a thread's column and edge slot are fixed (two 32-bit divisions per
+// thread instead of a 64-bit division per output vector).
 template <typename I>
-__global__ void u_add_v_vec_kernel(const I *__restrict__ src, const I *__restrict__ dst, int64_t n_edges, int32_t FV,
-                                   const float4 *__restrict__ l, const float4 *__restrict__ r, float4 *__restrict__ z) {
-  const int64_t total = n_edges * FV;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t e = t / FV;
-    const int c = (int)(t - e * FV);
-    const float4 a = __ldg(l + (int64_t)__ldg(src + e) * FV + c);
-    const float4 b = __ldg(r + (int64_t)__ldg(dst + e) * FV + c);
-    z[t] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+__global__ void __launch_bounds__(256) u_add_v_vec_kernel(const I *__restrict__ src, const I *__restrict__ dst, int64_t n_edges,
+                                                          int32_t FV, int32_t lanes, const float4 *__restrict__ l,
+                                                          const float4 *__restrict__ r, float4 *__restrict__ z) {
+  const int per_block = 256 / lanes;
+  const int slot = (int)threadIdx.x / lanes, c0 = (int)threadIdx.x - slot * lanes;
+  if (slot >= per_block) return;
+  for (int64_t e = (int64_t)blockIdx.x * per_block + slot; e < n_edges; e += (int64_t)gridDim.x * per_block) {
+    const float4 *a = l + (int64_t)__ldg(src + e) * FV, *b = r + (int64_t)__ldg(dst + e) * FV;
+    float4 *o = z + e * FV;
+    for (int c = c0; c < FV; c += lanes) {
+      const float4 p = __ldg(a + c), q = __ldg(b + c);
+      o[c] = make_float4(p.x + q.x, p.y + q.y, p.z + q.z, p.w + q.w);
+    }
   }
 }
 
@@ -38,10 +44,13 @@ template <typename I, bool VEC4>
 __global__ void u_dot_v_kernel(const I *__restrict__ src, const I *__restrict__ dst, int64_t n_edges, int32_t H,
                                int32_t D, const float *__restrict__ l, const float *__restrict__ r,
                                float *__restrict__ z) {
-  const int64_t total = n_edges * H;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t e = t / H;
-    const int h = (int)(t - e * H);
+  // min(H, 256) threads share an edge; a thread's head and edge slot are fixed (no 64-bit division per output)
+  const int lanes = H < 256 ? H : 256, per_block = 256 / lanes;
+  const int slot = (int)threadIdx.x / lanes, h0 = (int)threadIdx.x - slot * lanes;
+  if (slot >= per_block) return;
+  for (int64_t e = (int64_t)blockIdx.x * per_block + slot; e < n_edges; e += (int64_t)gridDim.x * per_block)
+  for (int h = h0; h < H; h += lanes) {
+    const int64_t t = e * H + h;
     const float *a = l + ((int64_t)__ldg(src + e) * H + h) * D;
     const float *b = r + ((int64_t)__ldg(dst + e) * H + h) * D;
     // products of fp32 values are exact in double and each addition errs by 2^-53: the dot product is exact to the
@@ -259,9 +268,10 @@ static int u_add_v(const I *src, const I *dst, int64_t n_edges, int64_t feat, co
   GPHL_REQUIRE(src && dst && l && r && z, "null pointer argument");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (feat % 4 == 0 && aligned16(l) && aligned16(r) && aligned16(z)) {
-    const int64_t total = n_edges * (feat / 4);
-    u_add_v_vec_kernel<I><<<grid_for(total, 256), 256, 0, stream>>>(
-        src, dst, n_edges, (int32_t)(feat / 4), reinterpret_cast<const float4 *>(l), reinterpret_cast<const float4 *>(r),
+    const int32_t fv = (int32_t)(feat / 4), lanes = std::min(fv, 256);
+    const int64_t per_block = 256 / lanes;
+    u_add_v_vec_kernel<I><<<grid_for((n_edges + per_block - 1) / per_block * 256, 256), 256, 0, stream>>>(
+        src, dst, n_edges, fv, lanes, reinterpret_cast<const float4 *>(l), reinterpret_cast<const float4 *>(r),
         reinterpret_cast<float4 *>(z));
     return launched("u_add_v_vec_kernel");
   }
@@ -299,10 +309,12 @@ static int u_dot_v(const I *src, const I *dst, int64_t n_edges, int64_t heads, i
       }
     }
   }
+  const int64_t per_block = 256 / std::min<int64_t>(heads, 256);
+  const unsigned grid = grid_for((n_edges + per_block - 1) / per_block * 256, 256);
   if (dim % 4 == 0 && aligned16(l) && aligned16(r)) {
-    u_dot_v_kernel<I, true><<<grid_for(total, 256), 256, 0, stream>>>(src, dst, n_edges, (int32_t)heads, (int32_t)dim, l, r, z);
+    u_dot_v_kernel<I, true><<<grid, 256, 0, stream>>>(src, dst, n_edges, (int32_t)heads, (int32_t)dim, l, r, z);
   } else {
-    u_dot_v_kernel<I, false><<<grid_for(total, 256), 256, 0, stream>>>(src, dst, n_edges, (int32_t)heads, (int32_t)dim, l, r, z);
+    u_dot_v_kernel<I, false><<<grid, 256, 0, stream>>>(src, dst, n_edges, (int32_t)heads, (int32_t)dim, l, r, z);
   }
   return launched("u_dot_v_kernel");
 }

@@ -378,173 +378,6 @@ __global__ void __launch_bounds__(TC_THREADS) segment_mm_tc_kernel(TcArgs a, con
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
-// ---- persistent form: one block walks several tiles -------------------------------------------------------------
-// With K <= 256 a tile is only two to four slabs, and what a block does before its first multiply (find its tile, read
-// the row indices, fetch the first rows of x and the first weight slab) and after its last one (drain the stores) is
-// most of a tile's time: with one tile per block only the other block on the SM hides it.  Here a block keeps its
-// tensor memory and barriers and takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the next tile is looked up while
-// the current one is multiplied, its first rows of x are requested before the current tile's epilogue starts, and its
-// first weight slab is copied in as soon as the last multiply of the current tile has finished.  One weight stage;
-// barrier phases run on a slab counter that continues across tiles.
-__global__ void __launch_bounds__(TC_THREADS, 2) segment_mm_tc_persistent_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap,
-                                                                                 int64_t n_tiles) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t s_bar, s_full;
-  __shared__ uint32_t s_tmem;
-  __shared__ int s_seg[2], s_row0[2], s_rows[2], s_failed;
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_slices = (a.Npad + TC_NMAX - 1) / TC_NMAX;
-  int64_t tile = blockIdx.x;
-  if (tile >= n_tiles) return;
-  if (warp == 0) {
-    if (lane == 0) s_rows[0] = 0, s_rows[1] = 0, s_failed = 0;
-    __syncwarp();
-    tile_lookup(a, tile / n_slices, lane, &s_seg[0], &s_row0[0], &s_rows[0]);
-  }
-  __syncthreads();
-  if (s_rows[0] == 0) return;                               // uniform: nothing allocated yet
-
-  const uint32_t acc_cols = a.box_rows <= 32 ? 32 : (a.box_rows <= 64 ? 64 : 128);   // widest column slice
-  const uint32_t tmem_cols = 2 * acc_cols;
-  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t *sA = smem, *sB = smem + 3 * A_SPLIT_BYTES;
-  const int b_split_bytes = a.box_rows * 128, b_stage_bytes = 3 * b_split_bytes;
-  const uint32_t bar = smem_u32(&s_bar), full = smem_u32(&s_full);
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(tmem_cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    if (lane == 0) {
-      mbar_init(bar, 1);
-      mbar_init(full, 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = s_tmem;
-
-  const int c = tid & 7;
-  const float *xrow[4];
-  bool rok[4];
-  auto setup_rows = [&](int row0, int rows) {               // this thread's 4 rows of the tile (optionally gathered)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = (tid >> 3) + 32 * i;
-      rok[i] = r < rows;
-      const int64_t src = rok[i] ? (a.gather ? __ldg(a.gather + row0 + r) : (int64_t)(row0 + r)) : 0;
-      xrow[i] = a.x + src * a.K;
-    }
-  };
-  float4 pre[4][2];
-  auto load_slab = [&](int k0) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int k = k0 + c * 8;
-      pre[i][0] = (rok[i] && k < a.K) ? __ldg(reinterpret_cast<const float4 *>(xrow[i] + k)) : make_float4(0, 0, 0, 0);
-      pre[i][1] = (rok[i] && k + 4 < a.K) ? __ldg(reinterpret_cast<const float4 *>(xrow[i] + k + 4)) : make_float4(0, 0, 0, 0);
-    }
-  };
-  const int nslabs = a.Kpad / TC_SLAB;
-  const int wplane = a.T * a.Npad;
-  int issued = 0, consumed = 0;                             // weight slabs: thread 0 only
-  auto issue_weights = [&](int seg, int n0, int slab) {
-    mbar_expect_tx(full, (uint32_t)b_stage_bytes);
-#pragma unroll
-    for (int sp = 0; sp < 3; ++sp)
-      tma_load_2d(smem_u32(sB) + sp * b_split_bytes, &wmap, slab * TC_SLAB, sp * wplane + seg * a.Npad + n0, full);
-    ++issued;
-  };
-
-  setup_rows(s_row0[0], s_rows[0]);
-  load_slab(0);
-  if (tid == 0) issue_weights(s_seg[0], (int)(tile % n_slices) * TC_NMAX, 0);
-  uint32_t g = 0;                                            // slabs committed so far by this block
-  for (int it = 0;; ++it) {
-    const int cur = it & 1, nxt = cur ^ 1;
-    const int seg = s_seg[cur], row0 = s_row0[cur], rows = s_rows[cur];
-    const int n0 = (int)(tile % n_slices) * TC_NMAX;
-    const int ncols = min(TC_NMAX, a.Npad - n0);
-    const uint32_t idesc = umma_idesc(ncols);
-    const int64_t next_tile = tile + gridDim.x;
-    if (warp == 0) {                                         // the next tile's place, read by everyone after the next barrier
-      if (lane == 0) s_rows[nxt] = 0;
-      __syncwarp();
-      if (next_tile < n_tiles) tile_lookup(a, next_tile / n_slices, lane, &s_seg[nxt], &s_row0[nxt], &s_rows[nxt]);
-    }
-    for (int s = 0; s < nslabs; ++s) {
-      if (g > 0 && !mbar_wait(bar, (g - 1) & 1)) s_failed = 1;     // previous slab (maybe of the previous tile) multiplied
-      if (tid == 0 && s > 0 && !s_failed) issue_weights(seg, n0, s);    // slab 0 was requested ahead
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = (tid >> 3) + 32 * i;
-        uint4 o1, o2, o3;
-        split3(pre[i][0].x, pre[i][0].y, o1.x, o2.x, o3.x);
-        split3(pre[i][0].z, pre[i][0].w, o1.y, o2.y, o3.y);
-        split3(pre[i][1].x, pre[i][1].y, o1.z, o2.z, o3.z);
-        split3(pre[i][1].z, pre[i][1].w, o1.w, o2.w, o3.w);
-        const int off = (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4 *>(sA + off) = o1;
-        *reinterpret_cast<uint4 *>(sA + A_SPLIT_BYTES + off) = o2;
-        *reinterpret_cast<uint4 *>(sA + 2 * A_SPLIT_BYTES + off) = o3;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (s + 1 < nslabs) load_slab((s + 1) * TC_SLAB);
-      __syncthreads();
-      if (s_failed) break;
-      if (tid == 0) {
-        const bool arrived = mbar_wait(full, g & 1);
-        ++consumed;
-        if (!arrived) s_failed = 1;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
-        const int pa[6] = {0, 2, 1, 0, 1, 0}, pb[6] = {2, 0, 1, 1, 0, 0};
-        if (arrived) {
-#pragma unroll
-          for (int p = 0; p < 6; ++p) {
-#pragma unroll
-            for (int kk = 0; kk < TC_SLAB / 16; ++kk) {
-              const uint64_t da = umma_desc(aA + pa[p] * A_SPLIT_BYTES + kk * 32);
-              const uint64_t db = umma_desc(aB + pb[p] * b_split_bytes + kk * 32);
-              if (p < 5) umma_bf16(tmem + acc_cols, da, db, idesc, (s > 0 || p > 0 || kk > 0) ? 1u : 0u);
-              else umma_bf16(tmem, da, db, idesc, (s > 0 || kk > 0) ? 1u : 0u);
-            }
-          }
-        }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-      }
-      ++g;
-      // after the last slab's rows were stored: request the next tile's first rows, to arrive during the epilogue
-      if (s + 1 == nslabs && s_rows[nxt] > 0) {
-        setup_rows(s_row0[nxt], s_rows[nxt]);
-        load_slab(0);
-      }
-    }
-    if (!s_failed && !mbar_wait(bar, (g - 1) & 1)) s_failed = 1;   // the tile's last multiply
-    const bool more = s_rows[nxt] > 0;
-    if (tid == 0 && more && !s_failed) issue_weights(s_seg[nxt], (int)(next_tile % n_slices) * TC_NMAX, 0);
-    __syncthreads();
-    if (s_failed) break;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    tile_epilogue(a, tmem, acc_cols, rows, row0, n0, ncols, sA, warp, lane);
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();                                         // staging buffer and accumulators are free again
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (!more) break;
-    tile = next_tile;
-  }
-  if (tid == 0) {
-    if (s_failed) atomicAdd(&g_tc_wait_timeouts, 1);
-    for (int j = consumed; j < issued; ++j) mbar_wait(full, (uint32_t)(j & 1));   // copies in flight must land first
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 0)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
-}
-
 }  // namespace gphl
 
 using namespace gphl;
@@ -636,19 +469,6 @@ extern "C" int gphl_segment_mm_tc_prepared_f32(const float *x, const void *works
   const int64_t row_tiles = (m + TC_M - 1) / TC_M + n_types;
   const int64_t blocks = row_tiles * ((npad + TC_NMAX - 1) / TC_NMAX);
   GPHL_REQUIRE(blocks <= 2147483647LL, "too many tiles");
-  if (knob("GPHL_TC_PERSIST", 0)) {
-    a.stages = 1;
-    const size_t smem1 = 1024 + 3 * (size_t)A_SPLIT_BYTES + stage_bytes;
-    cudaError_t e = cudaFuncSetAttribute(segment_mm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         1024 + 3 * A_SPLIT_BYTES + 3 * TC_NMAX * 128);
-    if (e != cudaSuccess) return fail(GPHL_ERR_CUDA, "segment_mm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int per_sm = std::max(1, knob("GPHL_TC_PERSIST", 0));
-    const int64_t grid = std::min<int64_t>(blocks, (int64_t)sms * per_sm);
-    segment_mm_tc_persistent_kernel<<<(unsigned)grid, TC_THREADS, smem1, stream>>>(a, wmap, blocks);
-    return launched("segment_mm_tc_persistent_kernel");
-  }
   segment_mm_tc_kernel<<<(unsigned)blocks, TC_THREADS, smem, stream>>>(a, wmap);
   return launched("segment_mm_tc_kernel");
 }

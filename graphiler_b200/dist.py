@@ -277,10 +277,9 @@ class ShardedLayer:
         piece is issued asynchronously right after its rows were produced and overlaps the next piece's ``fill``."""
         n_mine = self.num_owned
         if self.exchange == "halo" and self.push:
-            # One launch of the row-gather kernel per receiver and piece, the receivers taken in an order that makes
-            # every step of the loop a permutation of the ranks (no receiver is the target of two senders at once);
-            # the stores go through NVLink into the receiver's slot, on a second stream, while the next piece is
-            # projected.  Slots alternate between steps, so a sender that is one step ahead never overwrites rows a
+            # One launch of the multi-receiver row-scatter kernel per piece: it reads the projected rows from local
+            # memory and stores them through NVLink into every receiver's slot, dealing the rows so that concurrent
+            # stores go to different receivers; it runs on a second stream while the next piece is projected.  Slots alternate between steps, so a sender that is one step ahead never overwrites rows a
             # receiver is still aggregating: between two writes to the same slot lies the other slot's barrier, which
             # a receiver enters only after that aggregation was launched on the same stream.  The barrier is a
             # one-word NCCL all-reduce: stream-ordered, and it completes on a rank only when every rank's stores of
@@ -295,12 +294,14 @@ class ShardedLayer:
                     fill(r0, r1, self.proj[r0:r1])
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
+                    recv = []
                     for k in range(self.world):
                         peer = (self.rank + k) % self.world
                         a, b = self.push_cuts[peer][c], self.push_cuts[peer][c + 1]
                         if b > a:
-                            o = self.push_offset[peer] + (a - self.send_offsets[peer])
-                            capi.gather_rows(self.send_rows[a:b], self.proj, out=self.peer_bufs[peer][slot, o:o + (b - a)])
+                            recv.append((self.peer_bufs[peer][slot], self.push_offset[peer] + (a - self.send_offsets[peer]), a, b - a))
+                    if recv:
+                        capi.scatter_rows_peers(self.send_rows, self.proj, recv)
             self._mark("project")
             main.wait_stream(side)
             self._mark("pack")

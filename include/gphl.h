@@ -223,6 +223,15 @@ int gphl_gather_rows_i64(const int64_t *idx, const int64_t *idx2, int64_t n_out,
                          const void *x, void *y, void *stream);
 int gphl_gather_rows_i32(const int32_t *idx, const int32_t *idx2, int64_t n_out, int64_t row_bytes,
                          const void *x, void *y, void *stream);
+/* The sending side of a sparse row exchange, one launch for all receivers: receiver p gets rows
+ * x[idx[src_start[p] + k]], k in [0, count[p]), at rows dst_start[p] + k of its buffer dst[p].  A buffer may be
+ * another GPU's memory mapped into this process: the kernel reads local memory and writes with plain stores (no
+ * TMA, no multicast), and deals the rows so that concurrent stores go to different receivers.  The four arrays are
+ * host arrays of n_peers <= GPHL_MAX_PEERS entries; rows are multiples of 16 bytes.  No counterpart in the reference
+ * (single GPU). */
+#define GPHL_MAX_PEERS 16
+int gphl_scatter_rows_peers_i64(const int64_t *idx, int32_t n_peers, const int64_t *src_start, const int64_t *count,
+                                void *const *dst, const int64_t *dst_start, int64_t row_bytes, const void *x, void *stream);
 
 /* ---- typed linear: y[p_t:p_{t+1},:] = x[p_t:p_{t+1},:] @ w[t] ---------------------------
  * my_ops::SegmentMMNode / SegmentMMEdge (segment_mm.cu:4-33: a device-to-host copy of the

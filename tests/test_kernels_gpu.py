@@ -453,3 +453,20 @@ def test_general_gspmm_agrees_with_the_tuned_kernels_and_rejects_bad_arguments(g
         capi.gspmm("mul", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x)
     with pytest.raises(capi.GphlError):
         capi.gspmm("add", "sum", g.in_pointer, g.in_node_indices, g.in_edge_indices, u=x, e=torch.randn(g.num_edges, 5, device=DEV))
+
+
+def test_scatter_rows_to_several_receivers():
+    """The sending side of the sparse exchange on one GPU: three receive buffers, unequal counts (one empty), rows
+    taken through an index list; every receiver holds exactly its rows at its offset and nothing else is touched."""
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(500, 24, generator=gen).to(DEV)
+    idx = torch.randint(0, 500, (700,), generator=gen).to(DEV)
+    bufs = [torch.full((400, 24), -7.0, device=DEV) for _ in range(3)]
+    recv = [(bufs[0], 10, 0, 300), (bufs[1], 0, 300, 0), (bufs[2], 55, 300, 333)]
+    capi.scatter_rows_peers(idx, x, recv)
+    for b, first, pos, cnt in recv:
+        want = torch.full((400, 24), -7.0, device=DEV)
+        want[first:first + cnt] = x[idx[pos:pos + cnt]]
+        assert torch.equal(b, want)
+    with pytest.raises(capi.GphlError):
+        capi.scatter_rows_peers(idx, x, [(torch.zeros(4, 23, device=DEV), 0, 0, 1)])

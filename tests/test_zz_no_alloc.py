@@ -71,9 +71,16 @@ def test_noalloc_python_wrapper_and_capacity_limit():
                                               ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), None)
     assert rc == -4                                                   # GPHL_ERR_TOO_LARGE
     msg = lib.gphl_last_error().decode()
-    assert "exceeds" in msg and str(capi.SOFTMAX_NOALLOC_MAX_ROW_HEADS) in msg
+    assert "exceed" in msg and str(capi.SOFTMAX_NOALLOC_MAX_ROW_HEADS) in msg
     assert capi.launch_count() == before
     rc = lib.gphl_segment_softmax_noalloc_f32(ctypes.c_void_p(ptr.data_ptr()), ctypes.c_void_p(ptr.data_ptr()), 1 << 19, 4,
                                               ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), None)
     assert rc == -4
+    # a head count at the limit is refused by this entry point itself, with the same code (not passed on to be
+    # rejected as a generic size error), and a wrong output tensor never reaches the kernel
+    rc = lib.gphl_segment_softmax_noalloc_f32(ctypes.c_void_p(ptr.data_ptr()), ctypes.c_void_p(ptr.data_ptr()), 1, 1 << 20,
+                                              ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), None)
+    assert rc == -4
+    with pytest.raises(capi.GphlError):
+        capi.segment_softmax_noalloc(g.in_pointer, g.in_edge_indices, x, torch.empty(x.shape[0], 1, device=DEV))
     torch.cuda.synchronize()                                          # the context is still healthy
