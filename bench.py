@@ -221,6 +221,8 @@ def workload_config(g, args, world):
             "partition": ("none" if world == 1 else f"dst-rows x{world} (edge-balanced) + all-gather in {args.gather_chunks} overlapped pieces"
                           if args.exchange == "allgather" else f"dst-rows x{world} (edge-balanced) + "
                           + ("halo all-to-all of the rows each shard reads" if args.exchange == "halo" else
+                             "the rows each shard reads stored into its peer-mapped buffer over NVLink by the epilogue of the senders' projection kernel"
+                             if args.exchange == "fused" else
                              "the rows each shard reads stored into its peer-mapped buffer by the senders' row-gather kernel over NVLink")
                           + ", source rows " + ("dealt to the ranks by a hash of their id" if args.ownership != "blocks" else "owned in contiguous blocks")
                           + (f" (peer stores unavailable: {args.push_unavailable})" if getattr(args, "push_unavailable", None) else "")),
@@ -422,8 +424,8 @@ def run_native(args):
 
     sl = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, feat, dtype=dtype, rank=rank, world=world,
                             chunks=args.gather_chunks, exchange=args.exchange,
-                            ownership=(args.ownership if args.exchange in ("halo", "push") and args.ownership != "auto" else None))
-    if args.exchange == "push" and world > 1 and not sl.push:
+                            ownership=(args.ownership if args.exchange in ("halo", "push", "fused") and args.ownership != "auto" else None))
+    if args.exchange in ("push", "fused") and world > 1 and not sl.push:
         args.exchange = "halo"                       # symmetric memory unavailable: the all-to-all took over
         args.push_unavailable = sl.push_unavailable
     own = sl.owned_rows                              # source rows this rank projects (a block, or dealt by hash)
@@ -439,8 +441,10 @@ def run_native(args):
     kev = []
 
     def step(x_blk=x_blk):
-        def fill(q0, q1, dst):
-            if args.cublas_projection:
+        def fill(q0, q1, dst, fan=None):
+            if fan is not None:                      # fused exchange: the projection's epilogue stores to the receivers
+                layers.project(x_blk[q0:q1], w, nsrc_blk[q0:q1], out=dst, fan=fan)
+            elif args.cublas_projection:
                 if dst.dtype == x_blk.dtype:
                     torch.mm(x_blk[q0:q1], w, out=dst)
                     dst.mul_(nsrc_blk[q0:q1])
@@ -464,7 +468,7 @@ def run_native(args):
         step()
     sync()
     kev.clear()
-    if world > 1 and args.exchange in ("halo", "push"):
+    if world > 1 and args.exchange in ("halo", "push", "fused"):
         sl.phase_marks = []
     sampler = ClockSampler(local)
     if rank == 0:
@@ -635,12 +639,12 @@ def run_native(args):
         fb = lambda: gdist.gcn_layer_sharded(slb, xb, w, nsb, ndb)
         tb = torch.tensor([time_loop(fb, max(3, args.steps // 2), 3, sync)], device=dev, dtype=torch.float64)
         dist.all_reduce(tb, op=dist.ReduceOp.MAX)
-        extras["c5_gcn_bf16_storage"] = {"layer_ms": float(tb[0]), "exchange": "peer stores" if slb.push else slb.exchange}
+        extras["c5_gcn_bf16_storage"] = {"layer_ms": float(tb[0]), "exchange": "peer stores (row-scatter kernel)" if slb.push else slb.exchange}
         del slb
         torch.cuda.empty_cache()
         wl2 = synthetic.make_c5(scale=args.scale, device=dev)
         p2, hy = wl2.params, wl2.hyper
-        sparse = args.exchange in ("halo", "push")
+        sparse = args.exchange in ("halo", "push", "fused")
         slg = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, p2["fc_weight"].shape[1], rank=rank, world=world,
                                  exchange=args.exchange if sparse else "allgather")
         xg = (wl2.feats[slg.owned_rows] if sparse else wl2.feats[slg.block_range[0]:slg.block_range[1]]).contiguous()
@@ -652,7 +656,8 @@ def run_native(args):
         cg = yg.view(torch.int32).to(torch.int64).sum().reshape(1)
         dist.all_reduce(cg, op=dist.ReduceOp.SUM)
         extras["c5_gat"] = {"layer_ms": float(tg[0]),
-                            "exchange": ("peer stores of z, all-to-all of el / er" if slg.push else "all-to-all of z, el, er")
+                            "exchange": (("peer stores of z from the projection's epilogue" if slg.fused else "peer stores of z")
+                                         + ", all-to-all of el / er" if slg.push else "all-to-all of z, el, er")
                             if sparse else "allgather of z, el, er",
                             "output_checksum": f"{int(cg.item()) & 0xFFFFFFFFFFFFFFFF:016x}"}
         if rank == 0:
@@ -683,11 +688,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--ownership", default="auto", choices=["auto", "blocks", "hashed"],
                     help="halo exchange: which rank projects which source rows (auto = hashed)")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "halo", "push"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "halo", "push", "fused"],
                     help="N > 1: all-gather every projected row; halo = send each shard only the rows it reads (all-to-all); "
                          "push = the same rows stored straight into the receivers' peer-mapped buffers by the row-gather "
-                         "kernel, piece by piece under the projection (falls back to halo where symmetric memory is unavailable); "
-                         "auto = push (measured at 2 GPUs: 6.0 ms against 6.6 all-gather and 7.6 all-to-all)")
+                         "kernel, piece by piece under the projection; fused = stored by the projection kernel's own epilogue "
+                         "(both fall back to halo where symmetric memory is unavailable); "
+                         "auto = fused (measured at 2 GPUs: 5.2 ms fused, 5.6 push, 6.6 all-gather, 7.6 all-to-all)")
     ap.add_argument("--gather-chunks", type=int, default=4,
                     help="N > 1: pieces the projection + all-gather is cut into so that they overlap")
     ap.add_argument("--cublas-projection", action="store_true",
@@ -698,7 +704,7 @@ def main():
                     help="plain fp32 accumulation in the SpMM (default: compensated, the library's parity contract)")
     args = ap.parse_args()
     if args.exchange == "auto":
-        args.exchange = "push" if int(os.environ.get("WORLD_SIZE", "1")) >= 2 else "allgather"
+        args.exchange = "fused" if int(os.environ.get("WORLD_SIZE", "1")) >= 2 else "allgather"
     if args.warmup < 3 and args.impl == "native":
         args.warmup = 3
     return run_reference(args) if args.impl == "reference" else run_native(args)

@@ -49,6 +49,7 @@ SIGNATURES = {
     "gphl_sddmm_u_dot_v_f32_i32": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gphl_segment_mm_tc_prepare_weights": (c_int, [_P, c_int64, c_int64, c_int64, _P, _P]),
     "gphl_segment_mm_tc_prepared_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, c_int32, _P, _P]),
+    "gphl_segment_mm_tc_fanout_f32": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int32, _P, c_int32, _P, _P, _P, _P]),
     "gphl_scatter_rows_peers_i64": (c_int, [_P, c_int32, _P, _P, _P, _P, c_int64, _P, _P]),
     "gphl_gspmm_f32": (c_int, [c_int32, c_int32, _P, _P, _P, c_int64, c_int64, _P, c_int64, _P, c_int64, _P, _P, _P, _P, _P, _P]),
     "gphl_sddmm_u_dot_v_csc_f32": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
@@ -504,6 +505,44 @@ def linear(x, w, row_scale=None, relu: bool = False, out=None, workspace=None):
         ptr = _ONE_TYPE[key] = torch.tensor([0, x.shape[0]], dtype=torch.int32, device=x.device)
     return segment_mm(x, w.unsqueeze(0) if w.dim() == 2 else w, ptr, out=out, row_scale=row_scale, relu=relu,
                       tensor_cores=True, workspace=workspace, _weights_owner=w)
+
+
+class FanOut:
+    """Where the finished rows of a projection go besides its own output: ``bases`` (one (rows, n) float32 receive
+    buffer per receiver, possibly peer-mapped memory of another GPU), ``ptr`` ((m + 1) int32, device) and ``entry``
+    (int64, device: receiver << 40 | row in its buffer); see gphl_segment_mm_tc_fanout_f32."""
+
+    def __init__(self, bases, ptr, entry):
+        self.bases, self.ptr, self.entry = list(bases), ptr, entry
+
+
+def linear_fanout(x, w, fan: FanOut, row_scale=None, relu: bool = False, out=None):
+    """``relu?(row_scale * (x @ w))`` on the tensor cores with every finished row also stored into the receivers'
+    buffers from the kernel's epilogue (the sending side of the sparse exchange fused into the projection).  ``out``
+    may be None when the rows are not needed locally; returns ``out``."""
+    _dev(x, w, row_scale, out, fan.ptr, fan.entry)
+    m, k = x.shape
+    n = w.shape[-1]
+    if k % 4 != 0 or x.data_ptr() % 16 or (out is not None and out.data_ptr() % 16) or x.dtype != torch.float32:
+        raise GphlError("linear_fanout needs float32 rows of k % 4 == 0 columns, 16-byte aligned")
+    if fan.ptr.numel() != m + 1 or fan.ptr.dtype != torch.int32 or fan.entry.dtype != torch.int64:
+        raise GphlError("linear_fanout: fan.ptr must hold m + 1 int32 values, fan.entry int64")
+    for b in fan.bases:
+        if b.dtype != torch.float32 or _feat(b) != n or not b.is_contiguous():
+            raise GphlError("linear_fanout: receive buffers must be contiguous float32 matrices of n columns")
+    key = (x.device, m)
+    ptr = _ONE_TYPE.get(key)
+    if ptr is None:
+        ptr = _ONE_TYPE[key] = torch.tensor([0, m], dtype=torch.int32, device=x.device)
+    w3 = w.unsqueeze(0) if w.dim() == 2 else w
+    need = int(lib().gphl_segment_mm_tc_workspace_bytes(1, k, n))
+    bases = (c_void_p * len(fan.bases))(*[b.data_ptr() for b in fan.bases])
+    with torch.cuda.device(x.device):
+        ws = _prepared_weights(w, w3, 1, k, n, need, _stream(x))
+        _check(lib().gphl_segment_mm_tc_fanout_f32(_ptr(x), _ptr(ws), _ptr(ptr), 1, m, k, n, _ptr(row_scale), 1 if relu else 0,
+                                                   _ptr(out), len(fan.bases), bases, _ptr(fan.ptr), _ptr(fan.entry, fan.ptr),
+                                                   _stream(x)), "segment_mm_tc_fanout")
+    return out
 
 
 def tc_wait_timeouts() -> int:

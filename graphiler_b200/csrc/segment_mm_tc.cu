@@ -138,6 +138,12 @@ struct TcArgs {
   float *y;
   int64_t m;
   int32_t T, K, N, Kpad, Npad, relu;
+  // Optional fan-out of the finished rows (the sending side of a sparse exchange fused into the epilogue): output row
+  // i is also stored at row (entry & 0xffffffffff) of receiver (entry >> 40)'s buffer, for every entry in
+  // [fan_ptr[i], fan_ptr[i + 1]).  Receivers' buffers may be other GPUs' memory mapped into this process (plain stores).
+  const int32_t *fan_ptr;
+  const int64_t *fan_entry;
+  float *fan_base[GPHL_MAX_PEERS];
   int32_t stages;            // weight slabs in shared memory (1 or 2)
   int32_t box_rows;          // rows of one TMA box = min(128, Npad)
 };
@@ -207,14 +213,31 @@ __device__ __forceinline__ void tile_epilogue(const TcArgs &a, uint32_t tmem, ui
       const float4 o = *reinterpret_cast<const float4 *>(stg + rr * 128 + ((ch ^ (rr & 7)) << 4));
       const int grow = (warp & 3) * 32 + rr, col = n0 + c0 + ch * 4;
       if (grow < rows) {
-        float *dst = a.y + (int64_t)(row0 + grow) * a.N + col;
-        if (vec && col + 3 < a.N) {
-          __stcs(reinterpret_cast<float4 *>(dst), o);
-        } else {
-          const float oo[4] = {o.x, o.y, o.z, o.w};
+        const float oo[4] = {o.x, o.y, o.z, o.w};
+        if (a.y) {
+          float *dst = a.y + (int64_t)(row0 + grow) * a.N + col;
+          if (vec && col + 3 < a.N) {
+            __stcs(reinterpret_cast<float4 *>(dst), o);
+          } else {
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (col + e < a.N) dst[e] = oo[e];
+            for (int e = 0; e < 4; ++e)
+              if (col + e < a.N) dst[e] = oo[e];
+          }
+        }
+        if (a.fan_ptr) {
+          // the same 16 bytes to every receiver that reads this row; the 8 lanes of a row read the same entries
+          const int f1 = __ldg(a.fan_ptr + row0 + grow + 1);
+          for (int f = __ldg(a.fan_ptr + row0 + grow); f < f1; ++f) {
+            const int64_t ent = __ldg(a.fan_entry + f);
+            float *dst = a.fan_base[ent >> 40] + (ent & 0xffffffffffLL) * a.N + col;
+            if (vec && col + 3 < a.N) {
+              *reinterpret_cast<float4 *>(dst) = o;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (col + e < a.N) dst[e] = oo[e];
+            }
+          }
         }
       }
     }
@@ -425,13 +448,16 @@ extern "C" int gphl_segment_mm_tc_prepare_weights(const float *w, int64_t n_type
   return launched("split_weights_kernel");
 }
 
-extern "C" int gphl_segment_mm_tc_prepared_f32(const float *x, const void *workspace, const int32_t *type_pointer,
-                                               int64_t n_types, int64_t m, int64_t k, int64_t n, const int64_t *gather_idx,
-                                               const float *row_scale, int32_t relu, float *y, void *stream_) {
+static int tc_prepared(const float *x, const void *workspace, const int32_t *type_pointer, int64_t n_types, int64_t m,
+                       int64_t k, int64_t n, const int64_t *gather_idx, const float *row_scale, int32_t relu, float *y,
+                       int32_t n_peers, void *const *peer_base, const int32_t *fan_ptr, const int64_t *fan_entry,
+                       void *stream_) {
   GPHL_REQUIRE(n_types >= 0 && m >= 0 && k >= 0 && n >= 0, "negative size");
   GPHL_REQUIRE(m < INT32_MAX && k < (1 << 16) && n < (1 << 16) && n_types < (1 << 20), "size out of range");
   if (m == 0 || n == 0 || n_types == 0) return GPHL_OK;
-  GPHL_REQUIRE(x && type_pointer && y && workspace, "null pointer argument");
+  GPHL_REQUIRE(x && type_pointer && workspace && (y || fan_ptr), "null pointer argument");
+  GPHL_REQUIRE(!fan_ptr || (fan_entry && peer_base && n_peers >= 1 && n_peers <= GPHL_MAX_PEERS),
+               "segment_mm_tc: fan-out needs entries and between 1 and %d receiver buffers", GPHL_MAX_PEERS);
   if (k % 4 != 0 || k == 0 || !aligned16(x) || !aligned16(workspace) || !aligned16(y))
     return fail(GPHL_ERR_UNSUPPORTED, "segment_mm_tc needs k %% 4 == 0 and 16-byte aligned x, y and workspace");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -440,6 +466,12 @@ extern "C" int gphl_segment_mm_tc_prepared_f32(const float *x, const void *works
   a.x = x, a.ws = static_cast<const __nv_bfloat16 *>(workspace), a.ptr = type_pointer, a.gather = gather_idx;
   a.row_scale = row_scale, a.y = y, a.m = m, a.T = (int32_t)n_types, a.K = (int32_t)k, a.N = (int32_t)n;
   a.Kpad = kpad, a.Npad = npad, a.relu = relu;
+  a.fan_ptr = fan_ptr, a.fan_entry = fan_entry;
+  if (fan_ptr)
+    for (int i = 0; i < n_peers; ++i) {
+      GPHL_REQUIRE(peer_base[i] == nullptr || aligned16(peer_base[i]), "segment_mm_tc: receiver buffers must be 16-byte aligned");
+      a.fan_base[i] = static_cast<float *>(peer_base[i]);
+    }
   a.box_rows = std::min<int>(TC_NMAX, npad);
   // two weight slabs in shared memory where two blocks still share an SM (boxes of at most 64 rows: 1 + 48 + 2 x 24
   // KB); with 128-row boxes a second slab would leave one block per SM, and two blocks with one slab each overlap
@@ -471,6 +503,26 @@ extern "C" int gphl_segment_mm_tc_prepared_f32(const float *x, const void *works
   GPHL_REQUIRE(blocks <= 2147483647LL, "too many tiles");
   segment_mm_tc_kernel<<<(unsigned)blocks, TC_THREADS, smem, stream>>>(a, wmap);
   return launched("segment_mm_tc_kernel");
+}
+
+extern "C" int gphl_segment_mm_tc_prepared_f32(const float *x, const void *workspace, const int32_t *type_pointer,
+                                               int64_t n_types, int64_t m, int64_t k, int64_t n, const int64_t *gather_idx,
+                                               const float *row_scale, int32_t relu, float *y, void *stream_) {
+  GPHL_REQUIRE(y != nullptr || m == 0 || n == 0 || n_types == 0, "null pointer argument");
+  return tc_prepared(x, workspace, type_pointer, n_types, m, k, n, gather_idx, row_scale, relu, y, 0, nullptr, nullptr, nullptr,
+                     stream_);
+}
+
+// The typed linear with the sending side of a sparse row exchange fused into its epilogue: every finished 128-row
+// tile is stored, 128-byte row segment by row segment, to the rows of the receivers' buffers that read it (`y` may be
+// NULL when nobody needs the rows locally).  One kernel computes and sends; the receivers synchronise afterwards.
+extern "C" int gphl_segment_mm_tc_fanout_f32(const float *x, const void *workspace, const int32_t *type_pointer,
+                                             int64_t n_types, int64_t m, int64_t k, int64_t n, const float *row_scale,
+                                             int32_t relu, float *y, int32_t n_peers, void *const *peer_base,
+                                             const int32_t *fan_ptr, const int64_t *fan_entry, void *stream_) {
+  GPHL_REQUIRE(fan_ptr != nullptr || m == 0, "segment_mm_tc_fanout: fan_ptr is NULL");
+  return tc_prepared(x, workspace, type_pointer, n_types, m, k, n, nullptr, row_scale, relu, y, n_peers, peer_base, fan_ptr,
+                     fan_entry, stream_);
 }
 
 extern "C" int gphl_segment_mm_tc_f32(const float *x, const float *w, const int32_t *type_pointer, int64_t n_types,

@@ -88,14 +88,18 @@ class ShardedLayer:
         # after the other, so the all-gather of piece c runs while piece c+1 is being projected.  The gather buffer
         # is then piece-major - piece c of every rank, rank-major, then piece c+1 ... - so that each collective
         # fills one contiguous slab, and the shard's source indices are renumbered to that layout once, here.
-        if exchange not in ("allgather", "halo", "push"):
-            raise ValueError("exchange must be 'allgather', 'halo' or 'push'")
+        if exchange not in ("allgather", "halo", "push", "fused"):
+            raise ValueError("exchange must be 'allgather', 'halo', 'push' or 'fused'")
         # "push" is the halo exchange with the all-to-all replaced by this library's row-gather kernel storing the
         # requested rows straight into the receivers' buffers over NVLink (peer-mapped symmetric memory)
-        self.push = exchange == "push" and self.world > 1
+        # "fused" is "push" with the stores issued by the projection kernel's own epilogue: every finished 128-row tile
+        # goes straight to the receivers that read it, and no second kernel re-reads the projected rows
+        self.push = exchange in ("push", "fused") and self.world > 1
+        self.fused = exchange == "fused" and self.world > 1 and feat % 4 == 0 and dtype == torch.float32
         self.push_chunks = push_chunks
+        self.keep_projection = False    # fused form: also write the projected rows locally (layers that read them again)
         self.push_unavailable = None
-        if exchange == "push":
+        if exchange in ("push", "fused"):
             exchange = "halo"
         self.exchange = exchange if self.world > 1 else "allgather"
         self.phase_marks = None         # set to a list to have the halo path append (name, CUDA event) after each phase
@@ -225,8 +229,17 @@ class ShardedLayer:
                 cuts.append((torch.searchsorted(self.send_rows[a:b].contiguous(), bvec) + a).tolist())
             self.push_cuts = cuts                                    # push_cuts[peer][c]: first list position of piece c
             self._push_stream = torch.cuda.Stream(device=dev)
+            # fan-out table of the fused form: for every owned row, the (receiver, row in its buffer) pairs that read it
+            peer_of = torch.repeat_interleave(torch.arange(world, device=dev), torch.tensor(self.send_counts, device=dev))
+            pos = torch.arange(self.send_rows.numel(), device=dev)
+            first = torch.tensor(self.send_offsets[:-1], device=dev)[peer_of]
+            dst_row = torch.tensor(self.push_offset, device=dev)[peer_of] + (pos - first)
+            order = torch.argsort(self.send_rows, stable=True)
+            self.fan_entry = ((peer_of << 40) | dst_row)[order].contiguous()
+            counts = torch.bincount(self.send_rows, minlength=nm)
+            self.fan_ptr = torch.cat([torch.zeros(1, dtype=torch.int64, device=dev), torch.cumsum(counts, 0)]).to(torch.int32)
         except Exception as ex:  # noqa: BLE001 - any failure means "use the all-to-all"
-            self.push = False
+            self.push = self.fused = False
             self.push_unavailable = repr(ex)[:300]
 
     def exchange_rows(self, owned: torch.Tensor, which: str = "sources") -> torch.Tensor:
@@ -287,6 +300,15 @@ class ShardedLayer:
             from . import capi
             self._mark("start")
             slot, self.push_slot = self.push_slot, 1 - self.push_slot
+            if self.fused:
+                # the projection kernel stores every finished tile into the receivers' slots itself
+                fan = capi.FanOut([b[slot] for b in self.peer_bufs], self.fan_ptr, self.fan_entry)
+                fill(0, n_mine, self.proj[:n_mine] if self.keep_projection else None, fan)
+                self._mark("project")
+                self._mark("pack")
+                dist.all_reduce(self._push_token, group=self.group)
+                self._mark("exchange")
+                return self._symm_local[slot, :self.halo_rows]
             main, side = torch.cuda.current_stream(), self._push_stream
             for c in range(self.push_chunks):
                 r0, r1 = self.push_bounds[c], self.push_bounds[c + 1]
@@ -375,8 +397,11 @@ def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, nor
                       relu: bool = True, aggregate: Optional[Callable] = None):
     """One GCN layer on this rank: project the local source block, all-gather, aggregate the local
     destination rows.  ``feature_block`` holds rows ``sl.owned_rows`` of the node features."""
-    def fill(r0, r1, out):
-        if feature_block.is_cuda:
+    def fill(r0, r1, out, fan=None):
+        if fan is not None:                                             # fused: the epilogue sends the rows itself
+            from .layers import project
+            project(feature_block[r0:r1], weight, norm_src_block[r0:r1], out=out, fan=fan)
+        elif feature_block.is_cuda:
             from .layers import project
             if out.dtype == feature_block.dtype:
                 project(feature_block[r0:r1], weight, norm_src_block[r0:r1], out=out)   # straight into the gather slot
@@ -412,11 +437,13 @@ def gat_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, fc_weight, 
         scores = {k: torch.empty((sl.num_owned, heads), dtype=sdt, device=feature_block.device) for k in ("el", "er")}
         a_s, a_d = attn_src.contiguous(), attn_dst.contiguous()
 
-        def fill(r0, r1, out):                       # called once, or once per piece of the owned rows
+        sl.keep_projection = True                   # the head scores read the projected rows again
+
+        def fill(r0, r1, out, fan=None):             # called once, or once per piece of the owned rows
             if feature_block.is_cuda:
                 from . import capi
                 from .layers import project
-                z = project(feature_block[r0:r1], fc_weight, out=out)
+                z = project(feature_block[r0:r1], fc_weight, out=out, fan=fan)
                 capi.gat_head_scores(z, a_s, a_d, el=scores["el"][r0:r1], er=scores["er"][r0:r1])
             else:
                 z = torch.mm(feature_block[r0:r1], fc_weight)

@@ -65,9 +65,12 @@ def gcn_norms(pg: PreparedGraph):
     return deg.pow(-0.5).unsqueeze(1)
 
 
-def project(feature, weight, row_scale=None, out=None):
+def project(feature, weight, row_scale=None, out=None, fan=None):
     """Dense projection ``row_scale * (feature @ weight)``: the tensor-core kernel when the shape allows (the source
-    scaling then rides in its epilogue), cuBLAS otherwise."""
+    scaling then rides in its epilogue), cuBLAS otherwise.  ``fan`` (a ``capi.FanOut``): the finished rows are also
+    stored into the receivers' buffers from the kernel's epilogue, and ``out`` may then be None."""
+    if fan is not None:
+        return capi.linear_fanout(feature, weight, fan, row_scale=None if row_scale is None else row_scale.reshape(-1), out=out)
     if feature.shape[1] % 4 == 0 and feature.is_contiguous() and weight.is_contiguous():
         return capi.linear(feature, weight, row_scale=None if row_scale is None else row_scale.reshape(-1), out=out)
     h = torch.mm(feature, weight, out=out) if out is not None else torch.mm(feature, weight)

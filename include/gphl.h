@@ -34,6 +34,7 @@ extern "C" {
 #define GPHL_OK 0
 #define GPHL_ERR_INVALID_ARGUMENT (-1) /* null pointer, negative size, unsupported shape   */
 #define GPHL_ERR_CUDA (-2)             /* a CUDA runtime call or launch failed             */
+#define GPHL_MAX_PEERS 16              /* receivers of one multi-receiver launch           */
 #define GPHL_ERR_UNSUPPORTED (-3)      /* shape outside what the kernels cover             */
 #define GPHL_ERR_TOO_LARGE (-4)        /* exceeds a stated fixed capacity                   */
 
@@ -229,7 +230,6 @@ int gphl_gather_rows_i32(const int32_t *idx, const int32_t *idx2, int64_t n_out,
  * TMA, no multicast), and deals the rows so that concurrent stores go to different receivers.  The four arrays are
  * host arrays of n_peers <= GPHL_MAX_PEERS entries; rows are multiples of 16 bytes.  No counterpart in the reference
  * (single GPU). */
-#define GPHL_MAX_PEERS 16
 int gphl_scatter_rows_peers_i64(const int64_t *idx, int32_t n_peers, const int64_t *src_start, const int64_t *count,
                                 void *const *dst, const int64_t *dst_start, int64_t row_bytes, const void *x, void *stream);
 
@@ -263,6 +263,16 @@ int gphl_segment_mm_tc_prepare_weights(const float *w, int64_t n_types, int64_t 
 int gphl_segment_mm_tc_prepared_f32(const float *x, const void *workspace, const int32_t *type_pointer, int64_t n_types,
                                     int64_t m, int64_t k, int64_t n, const int64_t *gather_idx, const float *row_scale,
                                     int32_t relu, float *y, void *stream);
+/* The prepared typed linear with the sending side of a sparse row exchange fused into its epilogue (no counterpart in
+ * the single-GPU reference): output row i is stored, besides y (which may be NULL), at row (e & 0xffffffffff) of
+ * receiver (e >> 40)'s buffer peer_base[e >> 40] for every entry e = fan_entry[f], f in [fan_ptr[i], fan_ptr[i+1]).
+ * fan_ptr (m + 1 int32) and fan_entry (int64) are device arrays; peer_base is a host array of n_peers <=
+ * GPHL_MAX_PEERS device pointers, each a (rows, n) float matrix that may live in another GPU's memory mapped into this
+ * process.  The kernel reads local memory only and writes with plain stores (no TMA store, no multicast). */
+int gphl_segment_mm_tc_fanout_f32(const float *x, const void *workspace, const int32_t *type_pointer, int64_t n_types,
+                                  int64_t m, int64_t k, int64_t n, const float *row_scale, int32_t relu, float *y,
+                                  int32_t n_peers, void *const *peer_base, const int32_t *fan_ptr, const int64_t *fan_entry,
+                                  void *stream);
 /* Barrier waits that ran out inside tensor-core kernels since the library was loaded (0 in a
  * healthy process; each kernel wait is bounded and a block that gives up frees its tensor memory
  * and returns).  Synchronises the device. */

@@ -46,12 +46,12 @@ def _worker(rank, world, port, tmp):
     fulls = []
     # one collective per layer, three overlapped pieces, or the sparse (halo) exchange of only the rows a shard reads
     for chunks, exchange, ownership in ((1, "allgather", None), (3, "allgather", None), (1, "halo", None),
-                                        (1, "halo", "blocks"), (1, "push", None)):
+                                        (1, "halo", "blocks"), (1, "push", None), (1, "fused", None)):
         sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], dtype=torch.float64,
                              rank=rank, world=world, make_plan=False, chunks=chunks, exchange=exchange,
                              ownership=ownership)
-        if exchange == "push":                    # peer stores need GPUs: on CPU ranks it is the all-to-all, and says why
-            assert not sl.push and "CUDA" in sl.push_unavailable
+        if exchange in ("push", "fused"):         # peer stores need GPUs: on CPU ranks it is the all-to-all, and says why
+            assert not sl.push and not sl.fused and "CUDA" in sl.push_unavailable
         own = sl.owned_rows                       # a contiguous block, or (halo) rows dealt by a hash of their id
         r0, r1 = sl.shard.row0, sl.shard.row1
         y = gd.gcn_layer_sharded(sl, x[own], w, norm[own], norm[r0:r1], aggregate=aggregate)

@@ -49,6 +49,14 @@ def _worker(rank, world, port, tmp):
         yp = gd.gcn_layer_sharded(sp, x[sp.owned_rows].contiguous(), w, norm[sp.owned_rows].contiguous(),
                                   norm[sp.shard.row0:sp.shard.row1].contiguous())
         pushed_ok = pushed_ok and bool(torch.equal(sp.gather_outputs(yp), single))
+    # and with the stores issued by the projection kernel's own epilogue (one kernel computes and sends)
+    sf = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, exchange="fused")
+    for _ in range(3):
+        yf = gd.gcn_layer_sharded(sf, x[sf.owned_rows].contiguous(), w, norm[sf.owned_rows].contiguous(),
+                                  norm[sf.shard.row0:sf.shard.row1].contiguous())
+        pushed_ok = pushed_ok and bool(torch.equal(sf.gather_outputs(yf), single))
+    if rank == 0:
+        print("fused exchange:", "projection epilogue stores to peers" if sf.fused else "not fused", flush=True)
     if rank == 0:
         print("push exchange:", "peer stores" if sp.push else f"fell back to all-to-all ({sp.push_unavailable})", flush=True)
     # GAT on the same graph: z, el, er gathered, fused attention on the local rows
@@ -60,7 +68,7 @@ def _worker(rank, world, port, tmp):
     single_gat = layers.gat_layer(pg, x, p["fc_weight"], p["attn_src"], p["attn_dst"], 0.2)
     # GAT over the sparse exchange (all-to-all, then peer stores for the z rows)
     gat_sparse_ok = True
-    for ex in ("halo", "push"):
+    for ex in ("halo", "push", "fused"):
         sgh = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, p["fc_weight"].shape[1], rank=rank, world=world,
                               exchange=ex)
         for _ in range(2):

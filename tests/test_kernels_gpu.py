@@ -470,3 +470,41 @@ def test_scatter_rows_to_several_receivers():
         assert torch.equal(b, want)
     with pytest.raises(capi.GphlError):
         capi.scatter_rows_peers(idx, x, [(torch.zeros(4, 23, device=DEV), 0, 0, 1)])
+
+
+def test_projection_with_fan_out_epilogue():
+    """The dense projection that also stores its finished rows into receivers' buffers (the fused sending side of
+    the sparse exchange), on one GPU with local receive buffers: every receiver row named by the fan-out table holds
+    the projected row bit for bit, the local output is the plain projection, rows not named are untouched, and the
+    local output may be left out."""
+    gen = torch.Generator().manual_seed(9)
+    m, k, n = 700, 64, 96
+    x = torch.randn(m, k, generator=gen).to(DEV)
+    w = (torch.randn(k, n, generator=gen) * 0.2).to(DEV)
+    sc = (torch.rand(m, generator=gen) + 0.5).to(DEV)
+    plain = capi.linear(x, w, row_scale=sc)
+    # receiver 0 takes every third row, receiver 1 a random multiset of rows (a row may go to several places), row 5 nowhere
+    r0 = torch.arange(0, m, 3)
+    r1 = torch.randint(0, m, (900,), generator=gen)
+    r1 = r1[r1 != 5]
+    rows = torch.cat([r0, r1])
+    peer = torch.cat([torch.zeros_like(r0), torch.ones_like(r1)])
+    dst = torch.cat([torch.arange(r0.numel()) + 4, torch.arange(r1.numel())])
+    order = torch.argsort(rows, stable=True)
+    entry = ((peer << 40) | dst)[order].to(DEV)
+    ptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(torch.bincount(rows, minlength=m), 0)]).to(torch.int32).to(DEV)
+    bufs = [torch.full((r0.numel() + 10, n), -3.0, device=DEV), torch.full((r1.numel() + 1, n), -3.0, device=DEV)]
+    fan = capi.FanOut(bufs, ptr, entry)
+    out = torch.empty(m, n, device=DEV)
+    capi.linear_fanout(x, w, fan, row_scale=sc, out=out)
+    assert torch.equal(out, plain)
+    want0 = torch.full_like(bufs[0], -3.0)
+    want0[4:4 + r0.numel()] = plain[r0.to(DEV)]
+    want1 = torch.full_like(bufs[1], -3.0)
+    want1[:r1.numel()] = plain[r1.to(DEV)]
+    assert torch.equal(bufs[0], want0) and torch.equal(bufs[1], want1)
+    for b in bufs:
+        b.fill_(-3.0)
+    capi.linear_fanout(x, w, fan, row_scale=sc, out=None)                 # nobody needs the rows locally
+    assert torch.equal(bufs[0], want0) and torch.equal(bufs[1], want1)
+    assert capi.tc_wait_timeouts() == 0
