@@ -139,6 +139,24 @@ struct DGLGraph : torch::CustomClassHolder {
   void SetEtypeCOO(Tensor t) {
     TORCH_CHECK(t.size(0) == num_edges, "etype_COO must have num_edges entries");
     etype_COO = t;
+    build_pairs();
+  }
+  // The distinct (edge type, source node) pairs of a typed graph, grouped by type.  An edge-typed linear applied to
+  // gathered source rows (SegmentMMEdgeSrc) yields the same row for every edge of one pair: where the pairs are at
+  // most half as many as the edges it is computed once per pair and the rows are handed out to the edges.  Built
+  // here, in a setter, because torch::unique synchronises; operator calls stay free of synchronisation.
+  void build_pairs() {
+    pair_src = Tensor();
+    if (!etype_COO.has_value() || !etype_COO.value().is_cuda() || !COO_src.is_cuda() || num_edges == 0) return;
+    c10::cuda::CUDAGuard guard(COO_src.device());
+    Tensor key = etype_COO.value().to(torch::kInt64) * num_nodes + COO_src.to(torch::kInt64);
+    auto res = at::_unique2(key, /*sorted=*/true, /*return_inverse=*/true, /*return_counts=*/false);
+    Tensor uniq = std::get<0>(res);
+    if (uniq.size(0) * 2 > num_edges) return;                      // too few repeats to pay for the hand-out pass
+    Tensor ptype = at::floor_divide(uniq, num_nodes);
+    pair_src = (uniq - ptype * num_nodes).contiguous();
+    pair_pointer = at::searchsorted(ptype, torch::arange(num_etypes + 1, ptype.options())).to(torch::kInt32).contiguous();
+    edge_pair = std::get<1>(res).contiguous();
   }
 
   // Plan for the reduce side (rows = destinations) or the message side (rows = sources).  The plans were built in the
@@ -172,6 +190,7 @@ struct DGLGraph : torch::CustomClassHolder {
 
   int64_t num_nodes, num_edges, num_ntypes, num_etypes;
   Tensor edge_pos32, dst32, scratch_in, scratch_out;
+  Tensor pair_src, pair_pointer, edge_pair;      // see build_pairs()
   Tensor in_pointer, in_node_indices, in_edge_indices;
   Tensor out_pointer, out_node_indices, out_edge_indices;
   Tensor COO_src, COO_dst;
@@ -521,6 +540,11 @@ Tensor SegmentMMEdge(Tensor x, Tensor w, const GraphPtr &g) {
 // Not registered by the reference: BroadcastSrcNode fused into SegmentMMEdge (x holds node rows).
 Tensor SegmentMMEdgeSrc(Tensor x, Tensor w, const GraphPtr &g) {
   TORCH_CHECK(x.size(0) == g->num_nodes, "SegmentMMEdgeSrc: features must have num_nodes rows");
+  if (g->pair_src.defined() && g->etype_pointer.has_value()) {
+    // one product row per distinct (edge type, source) pair, then handed out to the edges: the same rows bit for bit
+    Tensor per_pair = segment_mm(x, w, g->pair_pointer, g->num_etypes, g->pair_src.size(0), g->pair_src, "SegmentMMEdgeSrc");
+    return gather_rows(per_pair, g->edge_pair, c10::nullopt);
+  }
   return segment_mm(x, w, g->etype_pointer, g->num_etypes, g->num_edges, g->COO_src, "SegmentMMEdgeSrc");
 }
 

@@ -202,3 +202,23 @@ def test_typed_linear_sees_in_place_weight_updates(ops):
     w.mul_(2.0)
     assert torch.equal(ops.SegmentMMNode(x, w, G), y1 * 2.0)
     close(y1, O.segment_mm(x.cpu(), (w / 2).cpu(), g.ntype_pointer), rtol=1e-5, atol=2e-6)
+
+
+def test_edge_typed_linear_on_gathered_rows_is_evaluated_per_pair(ops):
+    """SegmentMMEdgeSrc on a graph with few sources per relation (every (relation, source) pair has many edges) takes
+    the per-pair route inside the operator and must return, bit for bit, what the edge-typed linear returns on the
+    gathered rows."""
+    gen = torch.Generator().manual_seed(12)
+    n, per = 60, 900
+    src = torch.cat([torch.randint(0, 8, (per,), generator=gen), torch.randint(8, 20, (per,), generator=gen),
+                     torch.randint(0, 60, (per,), generator=gen)])
+    dst = torch.randint(0, n, (3 * per,), generator=gen)
+    g = attach_types(prepare_graph(src, dst, n), ntype_counts=[20, 40], etype_counts=[per, per, per])
+    G = to_obj(g)
+    for k, m in ((64, 48), (16, 16)):                       # tensor-core kernel, narrow kernel
+        x = torch.randn(n, k, generator=gen).to(DEV)
+        w = (torch.randn(3, k, m, generator=gen) * 0.2).to(DEV)
+        fused = ops.SegmentMMEdgeSrc(x, w, G)
+        unfused = ops.SegmentMMEdge(ops.BroadcastSrcNode(x, G), w, G)
+        assert fused.shape == (3 * per, m) and torch.equal(fused, unfused)
+        close(fused, O.segment_mm(x.cpu()[g.COO_src], w.cpu(), g.etype_pointer), rtol=1e-5, atol=2e-6)
