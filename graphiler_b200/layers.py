@@ -22,9 +22,17 @@ from .graph import GraphArrays
 
 
 class PreparedGraph:
-    def __init__(self, arrays: GraphArrays, max_feat: int = 256, chunk: int = capi.DEFAULT_CHUNK):
+    def __init__(self, arrays: GraphArrays, max_feat: int = 256, chunk: int = capi.DEFAULT_CHUNK, validate: bool = True):
         if not arrays.in_pointer.is_cuda:
             raise capi.GphlError("PreparedGraph needs device arrays: call GraphArrays.to('cuda') first")
+        if validate:
+            # the kernels trust these arrays: check them once, here (one pass on the device), as the TorchScript
+            # DGLGraph does in its constructor
+            n, e = arrays.num_nodes, arrays.num_edges
+            capi.validate_csr(arrays.in_pointer, arrays.in_node_indices, n, arrays.in_edge_indices, e)
+            capi.validate_csr(arrays.out_pointer, arrays.out_node_indices, n, arrays.out_edge_indices, e)
+            capi.validate_index(arrays.COO_src, n)
+            capi.validate_index(arrays.COO_dst, n)
         self.g = arrays
         self.chunk = chunk
         self._max_feat = max_feat

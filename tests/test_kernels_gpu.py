@@ -508,3 +508,26 @@ def test_projection_with_fan_out_epilogue():
     capi.linear_fanout(x, w, fan, row_scale=sc, out=None)                 # nobody needs the rows locally
     assert torch.equal(bufs[0], want0) and torch.equal(bufs[1], want1)
     assert capi.tc_wait_timeouts() == 0
+
+
+def test_graph_handle_validates_its_arrays():
+    """layers.PreparedGraph checks the arrays it is given once, on the device: an index out of range or a pointer array
+    that does not end at the edge count is an error, not an out-of-bounds read by a kernel later."""
+    import dataclasses
+    from graphiler_b200 import layers
+    g = hub_graph().to(DEV)
+    layers.PreparedGraph(g)                                             # a valid graph passes (also the empty one)
+    layers.PreparedGraph(GRAPHS["empty"]().to(DEV))
+    bad = dataclasses.replace(g, in_node_indices=g.in_node_indices.clone())
+    bad.in_node_indices[3] = g.num_nodes
+    with pytest.raises(capi.GphlError, match="neighbour index"):
+        layers.PreparedGraph(bad)
+    bad = dataclasses.replace(g, COO_dst=g.COO_dst.clone())
+    bad.COO_dst[0] = -1
+    with pytest.raises(capi.GphlError, match="index lies outside"):
+        layers.PreparedGraph(bad)
+    bad = dataclasses.replace(g, out_pointer=g.out_pointer.clone())
+    bad.out_pointer[-1] += 1
+    with pytest.raises(capi.GphlError, match="pointer array"):
+        layers.PreparedGraph(bad)
+    layers.PreparedGraph(bad, validate=False)                           # opt-out for arrays already known to be valid
