@@ -170,8 +170,15 @@ struct AccT<3> {
     }
   }
 };
+// Register budget: the kernel hides gather latency with resident warps, so for fp32 rows of up to 64 vectors the
+// allocation is capped where it was measured best - five blocks per SM for the unweighted sum (<= 51 registers), four
+// for the weighted ones (<= 64).  The other shapes (more vectors per lane, bf16 unpacking) would spill under that cap.
+template <typename T, int NV, int MODE>
+constexpr int gather_min_blocks() {
+  return (sizeof(T) == 4 && NV <= 2) ? (MODE == COPY ? 5 : 4) : 0;      // 0: no minimum, the compiler's own choice
+}
 template <typename T, int LPR, int NV, int MODE, int EXACT>
-__global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
+__global__ void __launch_bounds__(WARPS * 32, gather_min_blocks<T, NV, MODE>()) gather_sum_kernel(GatherArgs a) {
   constexpr int VEC = VecOf<T>::N;
   constexpr int G = 32 / LPR;              // neighbour rows streamed concurrently by one warp
   constexpr int U = (NV >= 4) ? 1 : 4 / NV;  // rows in flight per group: four 16-byte loads per lane (more costs occupancy)
@@ -208,7 +215,10 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
       if constexpr (EXACT) acc[v][k].lo = 0;
     }
 
-  const uint4 *x = static_cast<const uint4 *>(a.x);
+  // one multiply-add per edge forms a row's address: the lane's byte offset is folded into the base once, the second
+  // and later vectors of a lane lie at compile-time distances (LPR vectors apart)
+  const char *xb = static_cast<const char *>(a.x) + (size_t)(tile0 + l) * 16;
+  const uint32_t row_bytes = (uint32_t)a.FV * 16u;
   float *wsm = smem_w + (size_t)warp * 32 * a.H;
 
   int next_idx = 0;
@@ -270,9 +280,9 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
         for (int u = 0; u < U; ++u) {
           e[u] = jj + u * G + g;
           const int src = __shfl_sync(FULL, my_idx, e[u]);
-          const uint4 *row = x + (int64_t)src * a.FV;
+          const char *row = xb + (uint64_t)(uint32_t)src * row_bytes;
 #pragma unroll
-          for (int v = 0; v < NV; ++v) raw[u][v] = __ldg(row + cv[v]);
+          for (int v = 0; v < NV; ++v) raw[u][v] = __ldg(reinterpret_cast<const uint4 *>(row + v * (LPR * 16)));
         }
       } else {
 #pragma unroll
@@ -280,9 +290,10 @@ __global__ void __launch_bounds__(WARPS * 32) gather_sum_kernel(GatherArgs a) {
           e[u] = jj + u * G + g;
           const bool ok = e[u] < n;
           const int src = __shfl_sync(FULL, my_idx, e[u] & 31);
-          const uint4 *row = x + (int64_t)src * a.FV;
+          const char *row = xb + (uint64_t)(uint32_t)src * row_bytes;
 #pragma unroll
-          for (int v = 0; v < NV; ++v) raw[u][v] = (ok && cok[v]) ? __ldg(row + cv[v]) : make_uint4(0, 0, 0, 0);
+          for (int v = 0; v < NV; ++v)
+            raw[u][v] = (ok && cok[v]) ? __ldg(reinterpret_cast<const uint4 *>(row + v * (LPR * 16))) : make_uint4(0, 0, 0, 0);
         }
       }
 #pragma unroll
