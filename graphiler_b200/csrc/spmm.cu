@@ -71,6 +71,7 @@ struct AccT<1> : Acc2 {
   using Acc2::value;
   __device__ __forceinline__ void add(uint64_t v, int) { Acc2::add(v); }
   __device__ __forceinline__ void fma_exact(uint64_t p, uint64_t q, int) { Acc2::fma_exact(p, q); }
+  __device__ __forceinline__ void fma_w(uint64_t p, float w, double, int) { Acc2::fma_exact(p, pack2(w, w)); }
   __device__ __forceinline__ void merge(uint64_t ohi, uint64_t olo, int) { Acc2::merge(ohi, olo); }
   __device__ __forceinline__ uint64_t value(int) const { return Acc2::value(); }
   __device__ __forceinline__ void planes(float &h0, float &h1, float &l0, float &l1, int = 0) const {
@@ -84,6 +85,7 @@ struct AccT<0> {
   static constexpr uint64_t lo = 0;
   __device__ __forceinline__ void add(uint64_t v, int = 0) { hi = fadd2(hi, v); }
   __device__ __forceinline__ void fma_exact(uint64_t a, uint64_t b, int = 0) { hi = ffma2(a, b, hi); }
+  __device__ __forceinline__ void fma_w(uint64_t a, float w, double, int = 0) { hi = ffma2(a, pack2(w, w), hi); }
   __device__ __forceinline__ void merge(uint64_t ohi, uint64_t, int = 0) { hi = fadd2(hi, ohi); }
   __device__ __forceinline__ uint64_t value(int = 0) const { return hi; }
   __device__ __forceinline__ void planes(float &h0, float &h1, float &l0, float &l1, int = 0) const {
@@ -106,6 +108,12 @@ struct AccT<2> {
     unpack2(p, px, py);
     unpack2(q, qx, qy);
     hi = b(fma((double)px, (double)qx, d(hi))), lo = b(fma((double)py, (double)qy, d(lo)));
+  }
+  // both columns of the pair times one weight that was widened once (the conversions run on the slowest pipe)
+  __device__ __forceinline__ void fma_w(uint64_t p, float, double wd, int = 0) {
+    float px, py;
+    unpack2(p, px, py);
+    hi = b(fma((double)px, wd, d(hi))), lo = b(fma((double)py, wd, d(lo)));
   }
   __device__ __forceinline__ void merge(uint64_t ohi, uint64_t olo, int = 0) {
     hi = b(d(hi) + d(ohi)), lo = b(d(lo) + d(olo));
@@ -143,6 +151,17 @@ struct AccT<3> {
     } else {
       Acc2 t{hi, lo};
       t.fma_exact(p, q);
+      hi = t.hi, lo = t.lo;
+    }
+  }
+  __device__ __forceinline__ void fma_w(uint64_t p, float w, double wd, int k) {
+    if (in_double(k)) {
+      AccT<2> t{hi, lo};
+      t.fma_w(p, w, wd);
+      hi = t.hi, lo = t.lo;
+    } else {
+      Acc2 t{hi, lo};
+      t.fma_exact(p, pack2(w, w));
       hi = t.hi, lo = t.lo;
     }
   }
@@ -308,13 +327,14 @@ __global__ void __launch_bounds__(WARPS * 32, gather_min_blocks<T, NV, MODE>()) 
           } else {
             const float wgt = (e[u] < n) ? wsm[e[u] * a.H + head[v]] : 0.f;
             const uint64_t w2 = pack2(wgt, wgt);
+            const double wd = (double)wgt;                  // widened once per (edge, vector), not once per product
 #pragma unroll
             for (int k = 0; k < VP; ++k) {
               // attention weights are softmax probabilities: the rounded products sum to at most max|x| in
               // magnitude, so their rounding (<= eps/2 of that) is far below tolerance and only the sum is
               // compensated; arbitrary edge weights (u_mul_e_sum) keep the exact product
               if (MODE == GAT) acc[v][k].add(fmul2(val[k], w2), v * VP + k);
-              else acc[v][k].fma_exact(val[k], w2, v * VP + k);
+              else acc[v][k].fma_w(val[k], wgt, wd, v * VP + k);
             }
           }
         }
