@@ -424,7 +424,8 @@ __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int6
     const float2 st = __ldg(reinterpret_cast<const float2 *>(a.stats) + (int64_t)it.row * a.H + head);
     mx = st.x, inv = st.y;
   }
-  const uint4 *x = static_cast<const uint4 *>(a.x);
+  const char *xb = static_cast<const char *>(a.x) + (size_t)cv * 16;     // one multiply-add per row address
+  const uint32_t row_bytes = (uint32_t)a.FV * 16u;
   auto weight = [&](int i, int src) {
     if (MODE == MUL_E) {
       const int eid = a.eidx ? __ldg(a.eidx + i) : i;
@@ -451,7 +452,7 @@ __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int6
 #pragma unroll
     for (int u = 0; u < 4; ++u) src[u] = __ldg(a.idx + i + u);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) raw[u] = __ldg(x + (int64_t)src[u] * a.FV + cv);
+    for (int u = 0; u < 4; ++u) raw[u] = __ldg(reinterpret_cast<const uint4 *>(xb + (uint64_t)(uint32_t)src[u] * row_bytes));
 #pragma unroll
     for (int u = 0; u < 4; ++u) wgt[u] = (MODE == COPY) ? 1.f : weight(i + u, src[u]);
 #pragma unroll
@@ -459,7 +460,7 @@ __global__ void __launch_bounds__(256) gather_sum_rows_kernel(GatherArgs a, int6
   }
   for (; i < it.end; ++i) {
     const int src = __ldg(a.idx + i);
-    const uint4 raw = __ldg(x + (int64_t)src * a.FV + cv);
+    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xb + (uint64_t)(uint32_t)src * row_bytes));
     accumulate(raw, (MODE == COPY) ? 1.f : weight(i, src));
   }
   if (!cok) return;
