@@ -219,7 +219,9 @@ def workload_config(g, args, world):
             "nodes": g.num_nodes, "edges_incl_self_loops": g.num_edges, "feat": 256, "scale": args.scale,
             "storage": args.dtype, "accumulation": "fp32 plain" if getattr(args, "fast_accum", False) else "fp32 compensated (two-sum)",
             "partition": ("none" if world == 1 else f"dst-rows x{world} (edge-balanced) + all-gather in {args.gather_chunks} overlapped pieces"
-                          if args.exchange == "allgather" else f"dst-rows x{world} (edge-balanced) + "
+                          if args.exchange == "allgather" else f"dst-rows x{world} "
+                          + ("(dealt by the hash that deals the source rows: edges and rows read balanced)" if getattr(args, "destinations", "ranges") == "hashed"
+                             else "(edge-balanced ranges)") + " + "
                           + ("halo all-to-all of the rows each shard reads" if args.exchange == "halo" else
                              "the rows each shard reads stored into its peer-mapped buffer over NVLink by the epilogue of the senders' projection kernel"
                              if args.exchange == "fused" else
@@ -425,13 +427,13 @@ def run_native(args):
 
     sl = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, feat, dtype=dtype, rank=rank, world=world,
                             chunks=args.gather_chunks, exchange=args.exchange,
-                            ownership=(args.ownership if args.exchange in ("halo", "push", "fused") and args.ownership != "auto" else None))
+                            ownership=(args.ownership if args.exchange in ("halo", "push", "fused") and args.ownership != "auto" else None),
+                            destinations=args.destinations)
     if args.exchange in ("push", "fused") and world > 1 and not sl.push:
         args.exchange = "halo"                       # symmetric memory unavailable: the all-to-all took over
         args.push_unavailable = sl.push_unavailable
     own = sl.owned_rows                              # source rows this rank projects (a block, or dealt by hash)
-    r0, r1 = sl.shard.row0, sl.shard.row1
-    x_blk, nsrc_blk, ndst_loc = x[own].contiguous(), norm[own].contiguous(), norm[r0:r1].contiguous()
+    x_blk, nsrc_blk, ndst_loc = x[own].contiguous(), norm[own].contiguous(), norm[sl.dst_rows].contiguous()
     ndst_vec = ndst_loc.reshape(-1).contiguous()
     g_cpu = g.to("cpu") if (rank == 0 and world == 1 and not args.no_cpu) else None
     x_cpu = x.cpu() if g_cpu is not None else None
@@ -634,9 +636,9 @@ def run_native(args):
         del sl, out
         torch.cuda.empty_cache()
         slb = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, feat, dtype=torch.bfloat16, rank=rank, world=world,
-                                 chunks=args.gather_chunks, exchange=args.exchange)
+                                 chunks=args.gather_chunks, exchange=args.exchange, destinations=args.destinations)
         xb, nsb = x_blk, norm[slb.owned_rows].contiguous()      # the same rows: ownership depends on the exchange only
-        ndb = norm[slb.shard.row0:slb.shard.row1].contiguous()
+        ndb = norm[slb.dst_rows].contiguous()
         fb = lambda: gdist.gcn_layer_sharded(slb, xb, w, nsb, ndb)
         tb = torch.tensor([time_loop(fb, max(3, args.steps // 2), 3, sync)], device=dev, dtype=torch.float64)
         dist.all_reduce(tb, op=dist.ReduceOp.MAX)
@@ -647,7 +649,8 @@ def run_native(args):
         p2, hy = wl2.params, wl2.hyper
         sparse = args.exchange in ("halo", "push", "fused")
         slg = gdist.ShardedLayer(g.in_pointer, g.in_node_indices, n, p2["fc_weight"].shape[1], rank=rank, world=world,
-                                 exchange=args.exchange if sparse else "allgather")
+                                 exchange=args.exchange if sparse else "allgather",
+                                 destinations=args.destinations if sparse else "ranges")
         xg = (wl2.feats[slg.owned_rows] if sparse else wl2.feats[slg.block_range[0]:slg.block_range[1]]).contiguous()
         del wl2
         fg = lambda: gdist.gat_layer_sharded(slg, xg, p2["fc_weight"], p2["attn_src"], p2["attn_dst"], hy["slope"])
@@ -689,6 +692,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--ownership", default="auto", choices=["auto", "blocks", "hashed"],
                     help="halo exchange: which rank projects which source rows (auto = hashed)")
+    ap.add_argument("--destinations", default="auto", choices=["auto", "ranges", "hashed"],
+                    help="N > 1: destination rows of a rank = a contiguous edge-balanced range, or the rows the rank owns "
+                         "under the hash that deals the source rows (balances the rows every shard receives; "
+                         "auto = hashed with a sparse exchange and hashed source ownership)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "halo", "push", "fused"],
                     help="N > 1: all-gather every projected row; halo = send each shard only the rows it reads (all-to-all); "
                          "push = the same rows stored straight into the receivers' peer-mapped buffers by the row-gather "
@@ -706,6 +713,9 @@ def main():
     args = ap.parse_args()
     if args.exchange == "auto":
         args.exchange = "fused" if int(os.environ.get("WORLD_SIZE", "1")) >= 2 else "allgather"
+    if args.destinations == "auto":
+        args.destinations = ("hashed" if int(os.environ.get("WORLD_SIZE", "1")) >= 2 and args.exchange != "allgather"
+                             and args.ownership != "blocks" else "ranges")
     if args.warmup < 3 and args.impl == "native":
         args.warmup = 3
     return run_reference(args) if args.impl == "reference" else run_native(args)

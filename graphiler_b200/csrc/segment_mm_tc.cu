@@ -31,6 +31,8 @@ constexpr int TC_NMAX = 128;    // output columns per block = TMEM columns
 constexpr int TC_SLAB = 64;     // bf16 elements per 128-byte swizzle row
 constexpr int A_SPLIT_BYTES = TC_M * 128;          // one bf16 copy of the x slab
 constexpr uint32_t WAIT_LIMIT = 1u << 22;          // try_wait polls before giving up
+constexpr int FAN_CACHE = 256;                     // fan-out entries a warp keeps in shared memory at a time
+static_assert(8 * 4096 + 8 * FAN_CACHE * 8 <= 3 * A_SPLIT_BYTES, "staging buffers and entry caches share the x slab");
 
 __device__ int g_tc_wait_timeouts = 0;
 
@@ -181,6 +183,16 @@ __device__ __forceinline__ void tile_epilogue(const TcArgs &a, uint32_t tmem, ui
   const int chalf = ((ncols + 63) / 64) * 32;            // columns per warp group, multiple of 32
   const int cbeg = (warp >> 2) * chalf;
   const float scale = (a.row_scale && r < rows) ? __ldg(a.row_scale + row0 + r) : 1.f;
+  // fan-out: the entries of the warp's 32 rows are one contiguous range [e0, e1) of fan_entry; they are brought into
+  // shared memory with coalesced loads, FAN_CACHE at a time (behind the staging buffers in the x slab's memory),
+  // each tagged in bits 56.. with the row of the warp that owns it
+  int p0 = 0, p1 = 0, e0 = 0, e1 = 0, cached = -1;
+  uint64_t *ent = reinterpret_cast<uint64_t *>(sA + 8 * 4096 + warp * (FAN_CACHE * 8));
+  if (a.fan_ptr) {
+    p0 = __ldg(a.fan_ptr + row0 + min(r, rows));
+    p1 = __ldg(a.fan_ptr + row0 + min(r + 1, rows));
+    e0 = __shfl_sync(FULL, p0, 0), e1 = __shfl_sync(FULL, p1, 31);
+  }
   for (int c0 = cbeg; c0 < min(cbeg + chalf, ncols); c0 += 32) {
     uint32_t v[32], u[32];
     const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)c0;
@@ -224,19 +236,34 @@ __device__ __forceinline__ void tile_epilogue(const TcArgs &a, uint32_t tmem, ui
               if (col + e < a.N) dst[e] = oo[e];
           }
         }
-        if (a.fan_ptr) {
-          // the same 16 bytes to every receiver that reads this row; the 8 lanes of a row read the same entries
-          const int f1 = __ldg(a.fan_ptr + row0 + grow + 1);
-          for (int f = __ldg(a.fan_ptr + row0 + grow); f < f1; ++f) {
-            const int64_t ent = __ldg(a.fan_entry + f);
-            float *dst = a.fan_base[ent >> 40] + (ent & 0xffffffffffLL) * a.N + col;
-            if (vec && col + 3 < a.N) {
-              *reinterpret_cast<float4 *>(dst) = o;
-            } else {
+      }
+    }
+    if (a.fan_ptr) {
+      // every (row, receiver) entry of the warp's rows is one unit of work for a group of 8 lanes: the groups stay
+      // busy whatever the rows' fan-outs are, and no global load sits between two stores
+      const int ecol = n0 + c0 + ch * 4;
+      for (int cb = e0; cb < e1; cb += FAN_CACHE) {
+        const int n = min(e1 - cb, FAN_CACHE);
+        if (cb != cached) {
+          __syncwarp();                                          // the previous piece has been read by every lane
+          for (int i = lane; i < n; i += 32) ent[i] = (uint64_t)__ldg(a.fan_entry + cb + i);
+          __syncwarp();
+          for (int f = max(p0, cb); f < min(p1, cb + n); ++f) ent[f - cb] |= (uint64_t)lane << 56;   // owner row
+          __syncwarp();
+          cached = cb;
+        }
+        for (int i = lane >> 3; i < n; i += 4) {
+          const uint64_t en = ent[i];
+          const int rl = (int)(en >> 56);
+          const float4 o = *reinterpret_cast<const float4 *>(stg + rl * 128 + ((ch ^ (rl & 7)) << 4));
+          float *dst = a.fan_base[(en >> 40) & 0xffff] + (int64_t)(en & 0xffffffffffULL) * a.N + ecol;
+          if (vec && ecol + 3 < a.N) {
+            *reinterpret_cast<float4 *>(dst) = o;
+          } else {
+            const float oo[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-              for (int e = 0; e < 4; ++e)
-                if (col + e < a.N) dst[e] = oo[e];
-            }
+            for (int e = 0; e < 4; ++e)
+              if (ecol + e < a.N) dst[e] = oo[e];
           }
         }
       }

@@ -45,16 +45,18 @@ def block_rows(n: int, world: int) -> int:
 
 @dataclass
 class RowShard:
-    """The CSC slice of one destination-row range: rebased pointer, global source ids."""
-    row0: int
-    row1: int
-    pointer: torch.Tensor          # (row1-row0+1) int32, starts at 0
+    """The CSC slice of one rank's destination rows: rebased pointer, global source ids.  The rows are the
+    contiguous range [row0, row1), or - when ``rows`` is set - the listed rows (ascending ids; row0 / row1 are None)."""
+    row0: Optional[int]
+    row1: Optional[int]
+    pointer: torch.Tensor          # (num_rows + 1) int32, starts at 0
     node_indices: torch.Tensor     # (nnz_local) int32, global source node ids
-    edge0: int                     # first CSC position of the range (positions are global edge slots)
+    edge0: Optional[int]           # first CSC position of a contiguous range (positions are global edge slots)
+    rows: Optional[torch.Tensor] = None   # int64 global ids of the destination rows when they are not a range
 
     @property
     def num_rows(self):
-        return self.row1 - self.row0
+        return int(self.pointer.numel()) - 1
 
     @property
     def nnz(self):
@@ -67,6 +69,25 @@ def shard_rows(in_pointer: torch.Tensor, in_node_indices: torch.Tensor, row0: in
     return RowShard(row0, row1, ptr, in_node_indices[e0:e1].contiguous(), e0)
 
 
+def shard_listed_rows(in_pointer: torch.Tensor, in_node_indices: torch.Tensor, rows: torch.Tensor) -> RowShard:
+    """The CSC slice of the listed destination rows (int64, ascending), their segments copied one after the other."""
+    p64 = in_pointer.to(torch.int64)
+    start = p64[rows]
+    deg = p64[rows + 1] - start
+    ptr = torch.cat([torch.zeros(1, dtype=torch.int64, device=rows.device), torch.cumsum(deg, 0)])
+    total = int(ptr[-1])
+    if total >= 2 ** 31:
+        raise ValueError("a shard holds at most 2^31 - 1 edges")
+    pos = torch.arange(total, dtype=torch.int64, device=rows.device) + torch.repeat_interleave(start - ptr[:-1], deg)
+    return RowShard(None, None, ptr.to(torch.int32).contiguous(), in_node_indices[pos].contiguous(), None, rows)
+
+
+def hashed_owner(num_nodes: int, world: int, device) -> torch.Tensor:
+    """Rank that owns each node id under the multiplicative hash used to deal rows to the ranks."""
+    ids = torch.arange(num_nodes, dtype=torch.int64, device=device)
+    return (((ids * 2654435761) & 0xFFFFFFFF) >> 13) % world
+
+
 class ShardedLayer:
     """Per-rank state of one sharded layer: row shard, persistent all-gather buffer, plan.
 
@@ -77,13 +98,31 @@ class ShardedLayer:
 
     def __init__(self, in_pointer, in_node_indices, num_nodes: int, feat: int, dtype=torch.float32,
                  rank: Optional[int] = None, world: Optional[int] = None, group=None, make_plan: bool = True,
-                 chunks: int = 1, exchange: str = "allgather", ownership: Optional[str] = None, push_chunks: int = 4):
+                 chunks: int = 1, exchange: str = "allgather", ownership: Optional[str] = None, push_chunks: int = 4,
+                 destinations: str = "ranges"):
         self.group = group
         self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
         self.num_nodes, self.feat = num_nodes, feat
+        # Which destination rows a rank aggregates.  "ranges": contiguous, edge-balanced ranges (outputs concatenate in
+        # rank order).  "hashed": the rows the rank also owns as a source under the hash - every shard then holds the
+        # same mix of popular and unpopular rows, so the distinct source rows a shard reads (what it receives over
+        # NVLink each step) are balanced as well as its edges; with contiguous ranges the shard of the many
+        # low-degree rows reads 1.9 times the rows of the shard of the hubs, and its inbound link sets the pace of
+        # every sender.  A layer's output rows are then the rows the rank projects in the next layer.
+        if destinations not in ("ranges", "hashed"):
+            raise ValueError("destinations must be 'ranges' or 'hashed'")
+        if destinations == "hashed" and (exchange == "allgather" or ownership == "blocks"):
+            raise ValueError("destinations='hashed' goes with a sparse exchange and hashed source ownership")
+        self.destinations = destinations if self.world > 1 else "ranges"
         self.bounds = edge_balanced_row_ranges(in_pointer, self.world)
-        self.shard = shard_rows(in_pointer, in_node_indices, self.bounds[self.rank], self.bounds[self.rank + 1])
+        if self.destinations == "hashed":
+            owner = hashed_owner(num_nodes, self.world, in_pointer.device)
+            self.dst_rows = torch.nonzero(owner == self.rank).reshape(-1)                    # ascending ids
+            self.shard = shard_listed_rows(in_pointer, in_node_indices, self.dst_rows)
+        else:
+            self.shard = shard_rows(in_pointer, in_node_indices, self.bounds[self.rank], self.bounds[self.rank + 1])
+            self.dst_rows = torch.arange(self.shard.row0, self.shard.row1, dtype=torch.int64, device=in_pointer.device)
         # With chunks > 1 every rank's source block is cut into `chunks` pieces that are projected and gathered one
         # after the other, so the all-gather of piece c runs while piece c+1 is being projected.  The gather buffer
         # is then piece-major - piece c of every rank, rank-major, then piece c+1 ... - so that each collective
@@ -145,7 +184,7 @@ class ShardedLayer:
         n, world = self.num_nodes, self.world
         ids = torch.arange(n, dtype=torch.int64, device=dev)
         if self.ownership == "hashed":
-            owner_of = (((ids * 2654435761) & 0xFFFFFFFF) >> 13) % world           # multiplicative hash of the row id
+            owner_of = hashed_owner(n, world, dev)                                 # multiplicative hash of the row id
         else:
             owner_of = ids // self.block
         order = torch.argsort(owner_of, stable=True)                               # rows grouped by owner, ascending id
@@ -172,7 +211,7 @@ class ShardedLayer:
         self.shard.node_indices = torch.searchsorted(keys, owner_of[idx64] * n + idx64).to(torch.int32)
         # the destination rows of this shard, requested from their owners the same way (the GAT layer needs the
         # destination-side attention score of its own rows, which their owners compute): grouped by owner, then by id
-        dst_ids = torch.arange(self.shard.row0, self.shard.row1, dtype=torch.int64, device=dev)
+        dst_ids = self.dst_rows
         dkeys, dperm = torch.sort(owner_of[dst_ids] * n + dst_ids)
         dst_sorted = dst_ids[dperm]
         self.dst_recv_counts = torch.bincount(owner_of[dst_sorted], minlength=world).tolist()
@@ -247,6 +286,8 @@ class ShardedLayer:
         this shard reads, in the compact order its renumbered indices refer to; ``which="destinations"`` returns the
         rows of this shard's own destination range, in row order.  Halo exchanges only."""
         assert self.exchange == "halo"
+        if which == "destinations" and self.destinations == "hashed":
+            return owned                                   # a rank's destination rows are the rows it owns, in this order
         if which == "sources":
             rows, sc, rc = self.send_rows, self.send_counts, self.recv_counts
         else:
@@ -381,16 +422,28 @@ class ShardedLayer:
         return buf
 
     def gather_outputs(self, local_out: torch.Tensor) -> torch.Tensor:
-        """Concatenate every rank's output rows in rank order (testing / export helper)."""
+        """Every rank's output rows assembled in node-id order (testing / export helper): the ranges concatenated in
+        rank order, or the hashed rows put back at their ids."""
         if self.world == 1:
             return local_out
-        sizes = [self.bounds[i + 1] - self.bounds[i] for i in range(self.world)]
+        owner = order = None
+        if self.destinations == "hashed":
+            owner = hashed_owner(self.num_nodes, self.world, local_out.device)
+            sizes = torch.bincount(owner, minlength=self.world).tolist()
+            order = torch.argsort(owner, stable=True)                      # rank-major, ascending id within a rank
+        else:
+            sizes = [self.bounds[i + 1] - self.bounds[i] for i in range(self.world)]
         pad = max(sizes)                      # ranges differ in length: exchange equal-sized padded blocks, then trim
         mine = torch.zeros((pad,) + tuple(local_out.shape[1:]), dtype=local_out.dtype, device=local_out.device)
         mine[:local_out.shape[0]] = local_out
         outs = [torch.empty_like(mine) for _ in range(self.world)]
         dist.all_gather(outs, mine, group=self.group)
-        return torch.cat([o[:s] for o, s in zip(outs, sizes)], 0)
+        cat = torch.cat([o[:s] for o, s in zip(outs, sizes)], 0)
+        if order is None:
+            return cat
+        full = torch.empty_like(cat)
+        full[order] = cat
+        return full
 
 
 def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, norm_src_block, norm_dst_local,

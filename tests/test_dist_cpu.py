@@ -45,16 +45,20 @@ def _worker(rank, world, port, tmp):
 
     fulls = []
     # one collective per layer, three overlapped pieces, or the sparse (halo) exchange of only the rows a shard reads
-    for chunks, exchange, ownership in ((1, "allgather", None), (3, "allgather", None), (1, "halo", None),
-                                        (1, "halo", "blocks"), (1, "push", None), (1, "fused", None)):
+    # ... and the destination rows as contiguous ranges or dealt by the hash that deals the source rows
+    for chunks, exchange, ownership, destinations in (
+            (1, "allgather", None, "ranges"), (3, "allgather", None, "ranges"), (1, "halo", None, "ranges"),
+            (1, "halo", "blocks", "ranges"), (1, "push", None, "ranges"), (1, "fused", None, "ranges"),
+            (1, "halo", None, "hashed"), (1, "fused", None, "hashed")):
         sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], dtype=torch.float64,
                              rank=rank, world=world, make_plan=False, chunks=chunks, exchange=exchange,
-                             ownership=ownership)
+                             ownership=ownership, destinations=destinations)
+        if destinations == "hashed":
+            assert torch.equal(sl.dst_rows, sl.owned_rows) and sl.shard.rows is sl.dst_rows
         if exchange in ("push", "fused"):         # peer stores need GPUs: on CPU ranks it is the all-to-all, and says why
             assert not sl.push and not sl.fused and "CUDA" in sl.push_unavailable
         own = sl.owned_rows                       # a contiguous block, or (halo) rows dealt by a hash of their id
-        r0, r1 = sl.shard.row0, sl.shard.row1
-        y = gd.gcn_layer_sharded(sl, x[own], w, norm[own], norm[r0:r1], aggregate=aggregate)
+        y = gd.gcn_layer_sharded(sl, x[own], w, norm[own], norm[sl.dst_rows], aggregate=aggregate)
         fulls.append(sl.gather_outputs(y))
     full = fulls[0]
     assert all(torch.equal(fulls[0], f) for f in fulls[1:])
@@ -81,6 +85,18 @@ def _worker(rank, world, port, tmp):
     # host GEMMs of differently shaped row blocks may round differently in the last bit; the GPU test demands
     # bit equality, where every row's products are formed identically
     halo_gat_same = bool(torch.allclose(slh.gather_outputs(yh), full_gat, rtol=1e-12, atol=1e-14))
+    slx = gd.ShardedLayer(g1.in_pointer, g1.in_node_indices, g1.num_nodes, p1["fc_weight"].shape[1], dtype=torch.float64,
+                          rank=rank, world=world, make_plan=False, exchange="halo", destinations="hashed")
+    yx = gd.gat_layer_sharded(slx, c1.feats.double()[slx.owned_rows], p1["fc_weight"], p1["attn_src"], p1["attn_dst"], 0.2,
+                              aggregate=gat_aggregate)
+    halo_gat_same = halo_gat_same and bool(torch.allclose(slx.gather_outputs(yx), full_gat, rtol=1e-12, atol=1e-14))
+    for bad in (dict(exchange="allgather"), dict(exchange="halo", ownership="blocks")):
+        try:
+            gd.ShardedLayer(g1.in_pointer, g1.in_node_indices, g1.num_nodes, 8, rank=rank, world=world, make_plan=False,
+                            destinations="hashed", **bad)
+            halo_gat_same = False
+        except ValueError:
+            pass
     if rank == 0:
         h = (x @ w) * norm
         want = np.maximum(O.spmm_src(h.numpy(), g.in_pointer, g.in_node_indices) * norm.numpy(), 0)

@@ -55,6 +55,14 @@ def _worker(rank, world, port, tmp):
         yf = gd.gcn_layer_sharded(sf, x[sf.owned_rows].contiguous(), w, norm[sf.owned_rows].contiguous(),
                                   norm[sf.shard.row0:sf.shard.row1].contiguous())
         pushed_ok = pushed_ok and bool(torch.equal(sf.gather_outputs(yf), single))
+    # destination rows dealt by the hash that deals the source rows (balanced inbound traffic): same bits, at their ids
+    for ex in ("fused", "push", "halo"):
+        sx = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, exchange=ex,
+                             destinations="hashed")
+        for _ in range(2):
+            yx = gd.gcn_layer_sharded(sx, x[sx.owned_rows].contiguous(), w, norm[sx.owned_rows].contiguous(),
+                                      norm[sx.dst_rows].contiguous())
+            pushed_ok = pushed_ok and bool(torch.equal(sx.gather_outputs(yx), single))
     if rank == 0:
         print("fused exchange:", "projection epilogue stores to peers" if sf.fused else "not fused", flush=True)
     if rank == 0:
@@ -68,9 +76,9 @@ def _worker(rank, world, port, tmp):
     single_gat = layers.gat_layer(pg, x, p["fc_weight"], p["attn_src"], p["attn_dst"], 0.2)
     # GAT over the sparse exchange (all-to-all, then peer stores for the z rows)
     gat_sparse_ok = True
-    for ex in ("halo", "push", "fused"):
+    for ex, dests in (("halo", "ranges"), ("push", "ranges"), ("fused", "ranges"), ("fused", "hashed")):
         sgh = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, p["fc_weight"].shape[1], rank=rank, world=world,
-                              exchange=ex)
+                              exchange=ex, destinations=dests)
         for _ in range(2):
             ygh = gd.gat_layer_sharded(sgh, x[sgh.owned_rows].contiguous(), p["fc_weight"], p["attn_src"], p["attn_dst"], 0.2)
             gat_sparse_ok = gat_sparse_ok and bool(torch.equal(sgh.gather_outputs(ygh), single_gat))

@@ -510,6 +510,39 @@ def test_projection_with_fan_out_epilogue():
     assert capi.tc_wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("m,n,copies", [(300, 256, 11), (129, 90, 19), (40, 16, 3)])
+def test_projection_fan_out_with_many_entries_per_row(m, n, copies):
+    """More (row, receiver) entries than a warp keeps in shared memory at once (32 rows x ``copies`` > 256), a width
+    whose last columns leave through the scalar path, a last row tile that is not full, and rows without entries."""
+    gen = torch.Generator().manual_seed(m + n)
+    k = 32
+    x = torch.randn(m, k, generator=gen).to(DEV)
+    w = (torch.randn(k, n, generator=gen) * 0.2).to(DEV)
+    plain = capi.linear(x, w)
+    counts = torch.full((m,), copies, dtype=torch.int64)
+    counts[::7] = 0                                                       # every seventh row goes nowhere
+    counts[1::5] = 1
+    rows = torch.repeat_interleave(torch.arange(m), counts)
+    total = rows.numel()
+    peer = torch.randint(0, 3, (total,), generator=gen)
+    dst = torch.empty(total, dtype=torch.int64)
+    sizes = []
+    for p in range(3):
+        sel = peer == p
+        dst[sel] = torch.randperm(int(sel.sum()), generator=gen)
+        sizes.append(int(sel.sum()))
+    entry = ((peer << 40) | dst).to(DEV)
+    ptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(counts, 0)]).to(torch.int32).to(DEV)
+    bufs = [torch.full((s + 2, n), -3.0, device=DEV) for s in sizes]
+    capi.linear_fanout(x, w, capi.FanOut(bufs, ptr, entry), out=None)
+    for p in range(3):
+        sel = peer == p
+        want = torch.full_like(bufs[p], -3.0)
+        want[dst[sel].to(DEV)] = plain[rows[sel].to(DEV)]
+        assert torch.equal(bufs[p], want)
+    assert capi.tc_wait_timeouts() == 0
+
+
 def test_graph_handle_validates_its_arrays():
     """layers.PreparedGraph checks the arrays it is given once, on the device: an index out of range or a pointer array
     that does not end at the edge count is an error, not an out-of-bounds read by a kernel later."""
