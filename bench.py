@@ -4,8 +4,10 @@
 Headline workload (every N): the scale-sweep configuration, one GCN layer forward
 (256 -> 256, fp32) on a synthetic R-MAT graph with N = 2.4 M nodes and 60 M edges + self-loops:
 ``relu(D^-1/2 * SpMM_copy_u_sum(D^-1/2 * (X @ W)))``.  With more than one GPU the layer is
-partitioned by destination rows (edge-balanced), the projection by equal source blocks, with
-one NCCL all-gather of the projected features per step (strong scaling: the graph is fixed).
+partitioned by destination rows and the projection by source rows, both dealt to the ranks by one hash of the
+row id; the projected rows a shard reads are stored into its peer-mapped buffer over NVLink by the epilogue of
+the senders' projection kernel (``--exchange`` / ``--destinations`` select the all-to-all, the all-gather and
+contiguous ranges instead).  Strong scaling: the graph is fixed.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
                   [--scale S] [--dtype fp32|bf16] [--no-extras]
@@ -701,7 +703,7 @@ def main():
                          "push = the same rows stored straight into the receivers' peer-mapped buffers by the row-gather "
                          "kernel, piece by piece under the projection; fused = stored by the projection kernel's own epilogue "
                          "(both fall back to halo where symmetric memory is unavailable); "
-                         "auto = fused (measured at 2 GPUs: 5.2 ms fused, 5.6 push, 6.6 all-gather, 7.6 all-to-all)")
+                         "auto = fused (measured at 2 GPUs with destination ranges: 5.2 ms fused, 5.6 push, 6.6 all-gather, 7.6 all-to-all)")
     ap.add_argument("--gather-chunks", type=int, default=4,
                     help="N > 1: pieces the projection + all-gather is cut into so that they overlap")
     ap.add_argument("--cublas-projection", action="store_true",

@@ -13,8 +13,11 @@ to-do); this module is new functionality.  One process per GPU:
   source rows are then dealt to the ranks by a hash of their id (``owned_rows``), because on a power-law
   graph whose popular nodes have neighbouring ids a contiguous block would make one rank the sender of most
   of the traffic;
-* the row-split plan of a shard depends only on each row's own length, so concatenating the
-  shards' outputs in rank order reproduces the single-GPU result bit for bit.
+* with a sparse exchange the destination rows can be dealt by the same hash (``destinations="hashed"``): every
+  shard then reads about the same number of distinct source rows, where the contiguous range of the many
+  low-degree rows reads almost twice the rows of the range of the hubs and its inbound link sets every sender's pace;
+* the row-split plan of a shard depends only on each row's own length, so putting the shards' output rows back at
+  their ids (``gather_outputs``: concatenation in rank order for ranges) reproduces the single-GPU result bit for bit.
 """
 from __future__ import annotations
 
