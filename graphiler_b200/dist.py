@@ -102,7 +102,7 @@ class ShardedLayer:
     def __init__(self, in_pointer, in_node_indices, num_nodes: int, feat: int, dtype=torch.float32,
                  rank: Optional[int] = None, world: Optional[int] = None, group=None, make_plan: bool = True,
                  chunks: int = 1, exchange: str = "allgather", ownership: Optional[str] = None, push_chunks: int = 4,
-                 destinations: str = "ranges"):
+                 destinations: Optional[str] = None):
         self.group = group
         self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
@@ -113,6 +113,8 @@ class ShardedLayer:
         # NVLink each step) are balanced as well as its edges; with contiguous ranges the shard of the many
         # low-degree rows reads 1.9 times the rows of the shard of the hubs, and its inbound link sets the pace of
         # every sender.  A layer's output rows are then the rows the rank projects in the next layer.
+        if destinations is None:          # hashed wherever it is possible: a sparse exchange with hashed source rows
+            destinations = "hashed" if exchange != "allgather" and ownership != "blocks" else "ranges"
         if destinations not in ("ranges", "hashed"):
             raise ValueError("destinations must be 'ranges' or 'hashed'")
         if destinations == "hashed" and (exchange == "allgather" or ownership == "blocks"):

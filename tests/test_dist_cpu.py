@@ -47,14 +47,16 @@ def _worker(rank, world, port, tmp):
     # one collective per layer, three overlapped pieces, or the sparse (halo) exchange of only the rows a shard reads
     # ... and the destination rows as contiguous ranges or dealt by the hash that deals the source rows
     for chunks, exchange, ownership, destinations in (
-            (1, "allgather", None, "ranges"), (3, "allgather", None, "ranges"), (1, "halo", None, "ranges"),
-            (1, "halo", "blocks", "ranges"), (1, "push", None, "ranges"), (1, "fused", None, "ranges"),
-            (1, "halo", None, "hashed"), (1, "fused", None, "hashed")):
+            (1, "allgather", None, None), (3, "allgather", None, None), (1, "halo", None, "ranges"),
+            (1, "halo", "blocks", None), (1, "push", None, "ranges"), (1, "fused", None, "ranges"),
+            (1, "halo", None, None), (1, "fused", None, "hashed")):
         sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], dtype=torch.float64,
                              rank=rank, world=world, make_plan=False, chunks=chunks, exchange=exchange,
                              ownership=ownership, destinations=destinations)
-        if destinations == "hashed":
+        if destinations == "hashed" or (destinations is None and exchange == "halo" and ownership is None):
             assert torch.equal(sl.dst_rows, sl.owned_rows) and sl.shard.rows is sl.dst_rows
+        else:
+            assert sl.destinations == "ranges" and sl.shard.row1 - sl.shard.row0 == sl.dst_rows.numel()
         if exchange in ("push", "fused"):         # peer stores need GPUs: on CPU ranks it is the all-to-all, and says why
             assert not sl.push and not sl.fused and "CUDA" in sl.push_unavailable
         own = sl.owned_rows                       # a contiguous block, or (halo) rows dealt by a hash of their id
@@ -79,7 +81,7 @@ def _worker(rank, world, port, tmp):
     full_gat = sl1.gather_outputs(yg)
     # the same layer over the sparse exchange: z and el of the rows the shard reads, er of its own rows from their owners
     slh = gd.ShardedLayer(g1.in_pointer, g1.in_node_indices, g1.num_nodes, p1["fc_weight"].shape[1], dtype=torch.float64,
-                          rank=rank, world=world, make_plan=False, exchange="halo")
+                          rank=rank, world=world, make_plan=False, exchange="halo", destinations="ranges")
     yh = gd.gat_layer_sharded(slh, c1.feats.double()[slh.owned_rows], p1["fc_weight"], p1["attn_src"], p1["attn_dst"], 0.2,
                               aggregate=gat_aggregate)
     # host GEMMs of differently shaped row blocks may round differently in the last bit; the GPU test demands

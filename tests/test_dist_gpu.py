@@ -24,7 +24,7 @@ def _worker(rank, world, port, tmp):
     norm = g.in_degrees().clamp(min=1).float().pow(-0.5).unsqueeze(1)
     sl = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world)
     lo, hi = sl.block_range
-    r0, r1 = sl.shard.row0, sl.shard.row1
+    r0, r1 = sl.shard.row0, sl.shard.row1           # the all-gather keeps contiguous destination ranges
     y = gd.gcn_layer_sharded(sl, x[lo:hi].contiguous(), w, norm[lo:hi].contiguous(), norm[r0:r1].contiguous())
     full = sl.gather_outputs(y)
     pg = layers.PreparedGraph(g)
@@ -33,13 +33,13 @@ def _worker(rank, world, port, tmp):
     s4 = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, chunks=4)
     lo4, hi4 = s4.block_range
     y4 = gd.gcn_layer_sharded(s4, x[lo4:hi4].contiguous(), w, norm[lo4:hi4].contiguous(),
-                              norm[s4.shard.row0:s4.shard.row1].contiguous())
+                              norm[s4.dst_rows].contiguous())
     full4 = s4.gather_outputs(y4)
     # and with the sparse (halo) exchange: only the source rows a shard reads travel, through one all-to-all
     sh = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, exchange="halo")
     own = sh.owned_rows                             # source rows are dealt to the ranks by a hash of their id
     yh = gd.gcn_layer_sharded(sh, x[own].contiguous(), w, norm[own].contiguous(),
-                              norm[sh.shard.row0:sh.shard.row1].contiguous())
+                              norm[sh.dst_rows].contiguous())
     fullh = sh.gather_outputs(yh)
     # the same exchange with the rows stored straight into the receivers' peer-mapped buffers; three steps in a row
     # exercise the alternating receive slots.  Where symmetric memory cannot be set up it is the all-to-all again.
@@ -47,18 +47,21 @@ def _worker(rank, world, port, tmp):
     pushed_ok = True
     for _ in range(3):
         yp = gd.gcn_layer_sharded(sp, x[sp.owned_rows].contiguous(), w, norm[sp.owned_rows].contiguous(),
-                                  norm[sp.shard.row0:sp.shard.row1].contiguous())
+                                  norm[sp.dst_rows].contiguous())
         pushed_ok = pushed_ok and bool(torch.equal(sp.gather_outputs(yp), single))
     # and with the stores issued by the projection kernel's own epilogue (one kernel computes and sends)
     sf = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, exchange="fused")
     for _ in range(3):
         yf = gd.gcn_layer_sharded(sf, x[sf.owned_rows].contiguous(), w, norm[sf.owned_rows].contiguous(),
-                                  norm[sf.shard.row0:sf.shard.row1].contiguous())
+                                  norm[sf.dst_rows].contiguous())
         pushed_ok = pushed_ok and bool(torch.equal(sf.gather_outputs(yf), single))
-    # destination rows dealt by the hash that deals the source rows (balanced inbound traffic): same bits, at their ids
+    # the sparse exchanges deal the destination rows by the hash that deals the source rows unless told otherwise
+    # (balanced inbound traffic); contiguous edge-balanced ranges give the same bits
+    pushed_ok = pushed_ok and sf.destinations == "hashed" and sp.destinations == "hashed" and sl.destinations == "ranges"
     for ex in ("fused", "push", "halo"):
         sx = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, w.shape[1], rank=rank, world=world, exchange=ex,
-                             destinations="hashed")
+                             destinations="ranges")
+        pushed_ok = pushed_ok and sx.shard.row0 is not None
         for _ in range(2):
             yx = gd.gcn_layer_sharded(sx, x[sx.owned_rows].contiguous(), w, norm[sx.owned_rows].contiguous(),
                                       norm[sx.dst_rows].contiguous())
@@ -76,7 +79,7 @@ def _worker(rank, world, port, tmp):
     single_gat = layers.gat_layer(pg, x, p["fc_weight"], p["attn_src"], p["attn_dst"], 0.2)
     # GAT over the sparse exchange (all-to-all, then peer stores for the z rows)
     gat_sparse_ok = True
-    for ex, dests in (("halo", "ranges"), ("push", "ranges"), ("fused", "ranges"), ("fused", "hashed")):
+    for ex, dests in (("halo", None), ("push", None), ("fused", None), ("fused", "ranges")):
         sgh = gd.ShardedLayer(g.in_pointer, g.in_node_indices, g.num_nodes, p["fc_weight"].shape[1], rank=rank, world=world,
                               exchange=ex, destinations=dests)
         for _ in range(2):
