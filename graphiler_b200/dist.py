@@ -480,6 +480,19 @@ def gcn_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weight, nor
     return torch.relu_(y) if relu else y
 
 
+def gcn_stack_sharded(sl: ShardedLayer, feature_block: torch.Tensor, weights, norm_block, aggregate: Optional[Callable] = None):
+    """Several GCN layers in a row on one sharded graph (relu between the layers, none after the last; every layer
+    ``sl.feat`` wide).  Needs ``destinations="hashed"``: a rank's output rows are then the rows it owns as a source, in
+    the same order, so a layer's output is the next layer's ``feature_block`` as it stands and nothing is
+    redistributed between the layers.  ``norm_block`` holds the normaliser of the owned rows, used on both sides."""
+    if sl.world > 1 and sl.destinations != "hashed":
+        raise ValueError("stacked layers need destinations='hashed' (the output rows of a range are not the rows the rank projects)")
+    h = feature_block
+    for i, w in enumerate(weights):
+        h = gcn_layer_sharded(sl, h, w, norm_block, norm_block, relu=i + 1 < len(weights), aggregate=aggregate)
+    return h
+
+
 def gat_layer_sharded(sl: ShardedLayer, feature_block: torch.Tensor, fc_weight, attn_src, attn_dst, slope: float,
                       aggregate: Optional[Callable] = None):
     """One GAT layer on this rank: project the local source block (z, el, er), all-gather the three, then run the

@@ -66,6 +66,11 @@ def _worker(rank, world, port, tmp):
             yx = gd.gcn_layer_sharded(sx, x[sx.owned_rows].contiguous(), w, norm[sx.owned_rows].contiguous(),
                                       norm[sx.dst_rows].contiguous())
             pushed_ok = pushed_ok and bool(torch.equal(sx.gather_outputs(yx), single))
+    # two layers in a row over the fused exchange: the output rows of a rank are the rows it projects next
+    w2 = (torch.randn(w.shape[1], w.shape[1], generator=torch.Generator().manual_seed(3)) * 0.1).to(dev)
+    ys = gd.gcn_stack_sharded(sf, x[sf.owned_rows].contiguous(), [w, w2], norm[sf.owned_rows].contiguous())
+    single2 = layers.gcn_layer(pg, single, w2, norm, norm, relu=False)
+    pushed_ok = pushed_ok and bool(torch.equal(sf.gather_outputs(ys), single2))
     if rank == 0:
         print("fused exchange:", "projection epilogue stores to peers" if sf.fused else "not fused", flush=True)
     if rank == 0:
